@@ -253,6 +253,104 @@ int ssdk_verify(const void* logits_p, const void* logits_q, const int64_t* specu
                 int jit_speculate, int B, int K, int V, uint64_t seed, uint64_t step_id,
                 int32_t* n_accept, int64_t* recovery, void* scratch, void* stream);
 
+
+/* ---- layered ("hybrid") models ---------------------------------------------------
+ * A second model family beside the dense Llama / Qwen3 decoders above: a program of layers, each one token mixer
+ * (a recurrent matrix-state layer or latent attention) and an optional mixture-of-experts feed-forward that read the
+ * SAME normed input (parallel block), with per-channel layer scales.  The reference has no such model; these entry
+ * points follow the conventions of the ones above (caller-owned device memory, int return codes).
+ * Storage type T of weights / activations / latent cache: bf16 (fp32 accumulation; residual stream, norms, routers,
+ * attention scores, gates and recurrent state in fp32) or fp32 throughout (no TF32). */
+enum { SSDK_DT_F32 = 0, SSDK_DT_BF16 = 1 };
+enum { SSDK_MIX_WKV = 0, SSDK_MIX_MLSTM = 1, SSDK_MIX_LATENT_ATTN = 2 };
+enum { SSDK_MLP_NONE = 0, SSDK_MLP_MOE = 1 };
+
+/* tensors of a hybrid model (ssdk_hyb_bind); [out, in] row-major, storage type T */
+enum {
+  SSDK_HT_EMBED = 0,     /* [vocab, width]                       layer = -1 */
+  SSDK_HT_HEAD,          /* [vocab, width] */
+  SSDK_HT_FINAL_NORM,    /* [width] unit-offset weight */
+  SSDK_HT_NORM,          /* [width] unit-offset weight of the block's single norm */
+  SSDK_HT_LS_MIX,        /* [width] layer scale of the mixer branch */
+  SSDK_HT_LS_MLP,        /* [width] layer scale of the feed-forward branch */
+  /* wkv */
+  SSDK_HT_WKV_MU,        /* [5, width] token-shift coefficients, order r k v g w */
+  SSDK_HT_WKV_R, SSDK_HT_WKV_K, SSDK_HT_WKV_V, SSDK_HT_WKV_G,   /* [H*D, width] */
+  SSDK_HT_WKV_W1,        /* [decay_rank, width] */
+  SSDK_HT_WKV_W2,        /* [H*D, decay_rank] */
+  SSDK_HT_WKV_W0,        /* [H*D] */
+  SSDK_HT_WKV_U,         /* [H, D] */
+  /* mlstm */
+  SSDK_HT_MLSTM_IN,      /* [2 H D + 2 H V + 2 H, width]: q | k | v | g | i | f rows packed by the loader */
+  SSDK_HT_MLSTM_IB, SSDK_HT_MLSTM_FB,   /* [H] */
+  /* latent attention */
+  SSDK_HT_LAT_DOWN,      /* [q_rank + kv_rank + rot_dim, width]: dq | dkv rows packed by the loader */
+  SSDK_HT_LAT_QNORM,     /* [q_rank] */
+  SSDK_HT_LAT_KVNORM,    /* [kv_rank] */
+  SSDK_HT_LAT_UQ,        /* [H (D + R), q_rank] */
+  SSDK_HT_LAT_UKT,       /* [H, kv_rank, D]: per head W_uk^T (transposed by the loader) */
+  SSDK_HT_LAT_UV,        /* [H V, kv_rank] */
+  SSDK_HT_LAT_SINK,      /* [H] */
+  /* every mixer */
+  SSDK_HT_MIX_NORM,      /* [H V] channel weight after the per-head unit RMS (wkv, mlstm) */
+  SSDK_HT_MIX_OUT,       /* [width, H V] */
+  /* mixture of experts */
+  SSDK_HT_ROUTER,        /* [E, width] */
+  SSDK_HT_EXPERT_IN,     /* [E, 2 ff, width]: per expert gate rows then up rows */
+  SSDK_HT_EXPERT_OUT,    /* [E, width, ff] */
+  SSDK_HT_SHARED_IN,     /* [2 sff + 1, width]: gate | up | shared-gate row */
+  SSDK_HT_SHARED_OUT,    /* [width, sff] */
+  SSDK_HT_COUNT
+};
+
+typedef struct ssdk_hyb_layer_cfg {
+  int32_t mixer;        /* SSDK_MIX_* */
+  int32_t heads, dim, vdim;          /* per head: key (unrotated query/key for latent attention) and value size */
+  int32_t rot_dim, rot_dims;         /* latent attention: rotated part per head; how many of them RoPE turns */
+  int32_t kv_rank, q_rank;           /* latent sizes */
+  int32_t decay_rank;                /* wkv: rows of the decay bottleneck */
+  float   rot_base, attn_scale, gate_cap;
+  int32_t mlp;          /* SSDK_MLP_* */
+  int32_t experts, top, groups, keep;
+  int32_t ff, shared_ff;             /* shared_ff = 0: no shared expert */
+  float   route_scale, limit, shared_limit;
+} ssdk_hyb_layer_cfg;
+
+typedef struct ssdk_hyb_cfg {
+  int32_t width, vocab, n_layers, dtype;
+  float   eps;
+  int32_t max_tokens;        /* rows per forward call */
+  int32_t max_seqs;          /* sequences per forward call */
+  int32_t max_logit_rows;    /* rows whose logits one call can return */
+  int32_t block_size, max_blocks_per_seq;
+  int32_t reserved;
+} ssdk_hyb_cfg;
+
+typedef struct ssdk_hyb_engine* ssdk_hyb_handle;
+
+int ssdk_hyb_create(const ssdk_hyb_cfg* cfg, const ssdk_hyb_layer_cfg* layers, ssdk_hyb_handle* out);
+int ssdk_hyb_destroy(ssdk_hyb_handle h);
+int ssdk_hyb_bind(ssdk_hyb_handle h, int layer, int tensor, const void* dev_ptr, int64_t rows, int64_t cols);
+/* caller-owned pools: latent cache (per latent-attention layer [num_blocks, block_size, kv_rank + rot_dim] T, layers
+ * back to back), recurrent state (fp32, n_slots slots), workspace */
+int64_t ssdk_hyb_cache_bytes(ssdk_hyb_handle h, int64_t num_blocks);
+int64_t ssdk_hyb_state_bytes(ssdk_hyb_handle h, int64_t n_slots);
+int64_t ssdk_hyb_workspace_bytes(ssdk_hyb_handle h);
+int ssdk_hyb_bind_pools(ssdk_hyb_handle h, void* cache, int64_t num_blocks, void* state, int64_t n_slots,
+                        void* workspace, int64_t workspace_bytes);
+/* One forward over a ragged batch: sequence s brings rows cu[s] .. cu[s+1]-1 (tokens ids[...]) that continue it at
+ * position pos0[s]; its recurrent state lives in slot[s] (read only if pos0[s] > 0) and its latent rows in the pages
+ * tables[s, :] (-1 padded).  Logits (fp32, [n_want, vocab]) of the rows want_rows[] are copied to logits_host if it
+ * is not NULL; if temps is not NULL the same rows are sampled (Sampler semantics of ssdk_sample) into out_tokens.
+ * residual_host, if not NULL, receives the fp32 residual stream after every layer, [n_layers, M, width] (debug tap).
+ * All pointers are host pointers; the call blocks until the results are on the host. */
+int ssdk_hyb_forward(ssdk_hyb_handle h, int n_seqs, int n_tokens, const int32_t* ids, const int32_t* cu,
+                     const int32_t* pos0, const int32_t* slot, const int32_t* tables,
+                     int n_want, const int32_t* want_rows, float* logits_host,
+                     const float* temps, uint64_t seed, uint64_t step_id, int64_t* out_tokens,
+                     float* residual_host, void* stream);
+int64_t ssdk_hyb_launch_count(ssdk_hyb_handle h);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1658,3 +1658,8 @@ int ssdk_verify(const void* logits_p, const void* logits_q, const int64_t* specu
 }
 
 }  // extern "C"
+
+// ==========================================================================================
+// layered (hybrid) model family: its own handle type and entry points (ssdk_hyb_*)
+// ==========================================================================================
+#include "hybrid_engine.cuh"

@@ -1,0 +1,507 @@
+// hybrid_engine.cuh — host side of the layered (hybrid) model family: the layer program, the pools it addresses
+// (paged latent cache, recurrent-state slots, workspace) and the ragged forward that prefill portions and single decode
+// tokens share.  Included by engine.cu; uses its Launcher / error helpers.  Kernels: layer_ops.cuh, linear.cuh,
+// recurrent.cuh, latent_attention.cuh, moe.cuh; the sampler is sample_kernel of sampling.cuh.
+#pragma once
+#include "latent_attention.cuh"
+#include "layer_ops.cuh"
+#include "linear.cuh"
+#include "moe.cuh"
+#include "recurrent.cuh"
+
+struct HybTensor {
+  const void* p = nullptr;
+  int64_t rows = 0, cols = 0;
+};
+struct HybLayer {
+  ssdk_hyb_layer_cfg c;
+  HybTensor t[SSDK_HT_COUNT];
+  size_t state_off = 0;      // floats from the start of a slot
+  size_t cache_row = 0;      // row width (elements) of this layer's latent pool
+  size_t cache_rows_before = 0;  // sum of the row widths of the latent layers before this one
+  float* inv_freq = nullptr; // device, [rot_dims / 2]
+};
+
+struct ssdk_hyb_engine {
+  ssdk_hyb_cfg cfg;
+  std::vector<HybLayer> layers;
+  HybTensor embed, head, final_norm;
+  size_t esz = 2;            // sizeof(T)
+  size_t slot_floats = 0, cache_row_total = 0;
+  uint8_t* cache = nullptr; int64_t num_blocks = 0;
+  float* state = nullptr; int64_t n_slots = 0;
+  // workspace carve
+  int64_t ws_bytes = 0;
+  float *x = nullptr, *p0 = nullptr, *p1 = nullptr, *p2 = nullptr, *p3 = nullptr, *mix_out = nullptr;
+  void *h = nullptr, *mixes = nullptr, *t0 = nullptr, *t1 = nullptr;
+  float *rz = nullptr, *wts = nullptr, *eg = nullptr, *eo = nullptr, *sz = nullptr, *so = nullptr;
+  void *ey = nullptr, *sy = nullptr;
+  int *sel = nullptr, *apos = nullptr, *arow = nullptr, *tile_expert = nullptr, *tile_row0 = nullptr, *tile_rows = nullptr,
+      *n_tiles = nullptr, *n_rows = nullptr;
+  void* hn = nullptr; float* logits = nullptr; bf16* logits16 = nullptr; int64_t* tokens = nullptr; float* temps = nullptr;
+  int* meta = nullptr; size_t meta_ints = 0;
+  int max_tiles = 0;
+  // widths of the shared buffers (elements per row)
+  int w_p0 = 0, w_p1 = 0, w_p2 = 0, w_p3 = 0, w_t0 = 0, w_t1 = 0, w_e = 0, w_top = 0, w_ff2 = 0, w_ff = 0, w_sff2 = 0, w_sff = 0;
+  bool any_wkv = false;
+  int* h_meta = nullptr;     // pinned staging of the step's integers
+  int64_t launches = 0;
+  bool smem_attr_done = false;
+};
+
+static int hyb_derive(ssdk_hyb_engine* e) {
+  const ssdk_hyb_cfg& g = e->cfg;
+  size_t soff = 0, crow = 0;
+  auto up = [](int& a, long long b) { if (b > a) a = (int)b; };
+  for (auto& L : e->layers) {
+    const ssdk_hyb_layer_cfg& c = L.c;
+    const int H = c.heads, D = c.dim, V = c.vdim;
+    if (H < 1 || D < 1) return fail("hybrid layer: heads / dim must be positive");
+    L.state_off = soff;
+    if (c.mixer == SSDK_MIX_WKV) {
+      if (D > 1024 || (size_t)(D * D + 5 * D) * 4 > 200 * 1024) return fail("wkv: head dim %d too large for the resident-state scan", D);
+      soff += (size_t)H * D * D + g.width;
+      up(e->w_p0, 5LL * H * D); up(e->w_p1, c.decay_rank); up(e->w_p2, (long long)H * D);
+      up(e->w_t0, c.decay_rank); up(e->w_t1, (long long)H * D);
+      e->any_wkv = true;
+    } else if (c.mixer == SSDK_MIX_MLSTM) {
+      if (V < 1 || std::max(D, V) > 1024 || (size_t)(D * V + 3 * D) * 4 > 200 * 1024) return fail("mlstm: head sizes %d x %d too large", D, V);
+      soff += (size_t)H * D * V + (size_t)H * D + H;
+      up(e->w_p0, 2LL * H * D + 2LL * H * V + 2 * H); up(e->w_p2, (long long)H * V); up(e->w_t1, (long long)H * V);
+    } else if (c.mixer == SSDK_MIX_LATENT_ATTN) {
+      if (c.rot_dims > c.rot_dim || (c.rot_dims & 1)) return fail("latent attention: rot dims %d of %d", c.rot_dims, c.rot_dim);
+      L.cache_row = (size_t)c.kv_rank + c.rot_dim;
+      L.cache_rows_before = crow;
+      crow += L.cache_row;
+      up(e->w_p0, (long long)c.q_rank + c.kv_rank + c.rot_dim); up(e->w_p1, (long long)H * (D + c.rot_dim));
+      up(e->w_p2, (long long)H * c.rot_dim); up(e->w_p3, (long long)H * c.kv_rank);
+      up(e->w_t0, std::max((long long)c.q_rank, (long long)H * c.kv_rank)); up(e->w_t1, std::max((long long)H * D, (long long)H * V));
+    } else {
+      return fail("hybrid layer: unknown mixer %d", c.mixer);
+    }
+    if (c.mlp == SSDK_MLP_MOE) {
+      if (c.experts < 1 || c.experts > kRouterMaxE) return fail("moe: 1 <= experts <= %d", kRouterMaxE);
+      if (c.groups < 1 || c.experts % c.groups) return fail("moe: %d experts do not form %d equal groups", c.experts, c.groups);
+      if (c.keep < 1 || c.keep > c.groups) return fail("moe: keep %d of %d groups", c.keep, c.groups);
+      if (c.top < 1 || c.top > 32 || c.top > c.keep * (c.experts / c.groups)) return fail("moe: top %d does not fit the kept groups", c.top);
+      up(e->w_e, c.experts); up(e->w_top, c.top); up(e->w_ff2, 2LL * c.ff); up(e->w_ff, c.ff);
+      if (c.shared_ff > 0) { up(e->w_sff2, 2LL * c.shared_ff + 1); up(e->w_sff, c.shared_ff); }
+    } else if (c.mlp != SSDK_MLP_NONE) {
+      return fail("hybrid layer: unknown feed-forward kind %d", c.mlp);
+    }
+  }
+  e->slot_floats = soff;
+  e->cache_row_total = crow;
+  return 0;
+}
+
+// workspace carve: base == nullptr only sizes it
+static int64_t hyb_carve(ssdk_hyb_engine* e, uint8_t* base) {
+  const ssdk_hyb_cfg& g = e->cfg;
+  const size_t cap = g.max_tokens, A = cap * (size_t)std::max(1, e->w_top), es = e->esz;
+  size_t off = 0;
+  auto take = [&](size_t bytes) { uint8_t* p = base ? base + off : nullptr; off = align_up(off + bytes, 256); return p; };
+  e->x = (float*)take(cap * g.width * 4);
+  e->h = take(cap * g.width * es);
+  e->mixes = take(e->any_wkv ? 5 * cap * g.width * es : 0);
+  e->p0 = (float*)take(cap * e->w_p0 * 4);
+  e->p1 = (float*)take(cap * e->w_p1 * 4);
+  e->p2 = (float*)take(cap * e->w_p2 * 4);
+  e->p3 = (float*)take(cap * e->w_p3 * 4);
+  e->t0 = take(cap * e->w_t0 * es);
+  e->t1 = take(cap * e->w_t1 * es);
+  e->mix_out = (float*)take(cap * g.width * 4);
+  e->rz = (float*)take(cap * e->w_e * 4);
+  e->wts = (float*)take(A * 4);
+  e->sel = (int*)take(A * 4); e->apos = (int*)take(A * 4); e->arow = (int*)take(A * 4);
+  e->max_tiles = (int)(A / kLinBM + e->w_e + 1);
+  e->tile_expert = (int*)take(e->max_tiles * 4); e->tile_row0 = (int*)take(e->max_tiles * 4);
+  e->tile_rows = (int*)take(e->max_tiles * 4);
+  e->n_tiles = (int*)take(4); e->n_rows = (int*)take(4);
+  e->eg = (float*)take(A * e->w_ff2 * 4);
+  e->ey = take(A * e->w_ff * es);
+  e->eo = (float*)take(e->w_e ? A * g.width * 4 : 0);
+  e->sz = (float*)take(cap * e->w_sff2 * 4);
+  e->sy = take(cap * e->w_sff * es);
+  e->so = (float*)take(e->w_sff ? cap * g.width * 4 : 0);
+  const size_t lr = g.max_logit_rows;
+  e->hn = take(lr * g.width * es);
+  e->logits = (float*)take(lr * g.vocab * 4);
+  e->logits16 = (bf16*)take(lr * g.vocab * 2);
+  e->tokens = (int64_t*)take(lr * 8);
+  e->temps = (float*)take(lr * 4);
+  e->meta_ints = 2 * cap + 3 * (size_t)g.max_seqs + 1 + (size_t)g.max_seqs * g.max_blocks_per_seq + lr;
+  e->meta = (int*)take(e->meta_ints * 4);
+  return (int64_t)off;
+}
+
+template <typename T>
+struct HybRun {
+  ssdk_hyb_engine* e;
+  Launcher L;
+  ssdk::Ragged rg;
+  int M;
+
+  template <typename OutT>
+  int lin_args(const ssdk::LinearArgs& a, int rows_hint, int batch) {
+    dim3 grid((a.N + ssdk::kLinBN - 1) / ssdk::kLinBN, a.tile_expert ? e->max_tiles : (rows_hint + ssdk::kLinBM - 1) / ssdk::kLinBM, batch);
+    return L.go(ssdk::linear_kernel<T, OutT>, grid, dim3(ssdk::kLinThreads), 0, a);
+  }
+  // C[M, N] (fp32 unless out_t) = A[M, K] W[N, K]^T
+  int lin(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int m, int N, int K, bool out_t = false,
+          int batch = 1, long long sA = 0, long long sW = 0, long long sC = 0) {
+    ssdk::LinearArgs a = {};
+    a.A = A; a.W = W; a.C = C; a.M = m; a.N = N; a.K = K; a.lda = lda; a.ldw = ldw; a.ldc = ldc;
+    a.sA = sA; a.sW = sW; a.sC = sC;
+    return out_t ? lin_args<T>(a, m, batch) : lin_args<float>(a, m, batch);
+  }
+  int check_tensor(const HybLayer& Lr, int id, int64_t rows, int64_t cols, const char* name) {
+    const HybTensor& t = Lr.t[id];
+    if (!t.p) return fail("hybrid: tensor %s not bound", name);
+    if (t.rows * t.cols != rows * cols) return fail("hybrid: tensor %s has %lld x %lld elements, expected %lld x %lld", name,
+                                                     (long long)t.rows, (long long)t.cols, (long long)rows, (long long)cols);
+    return 0;
+  }
+
+  int wkv(HybLayer& Lr) {
+    const ssdk_hyb_layer_cfg& c = Lr.c;
+    const int H = c.heads, D = c.dim, HD = H * D, W = e->cfg.width;
+    CKI(check_tensor(Lr, SSDK_HT_WKV_MU, 5, W, "wkv.mu")); CKI(check_tensor(Lr, SSDK_HT_WKV_R, HD, W, "wkv.r"));
+    CKI(check_tensor(Lr, SSDK_HT_WKV_K, HD, W, "wkv.k")); CKI(check_tensor(Lr, SSDK_HT_WKV_V, HD, W, "wkv.v"));
+    CKI(check_tensor(Lr, SSDK_HT_WKV_G, HD, W, "wkv.g")); CKI(check_tensor(Lr, SSDK_HT_WKV_W1, c.decay_rank, W, "wkv.w1"));
+    CKI(check_tensor(Lr, SSDK_HT_WKV_W2, HD, c.decay_rank, "wkv.w2")); CKI(check_tensor(Lr, SSDK_HT_WKV_W0, HD, 1, "wkv.w0"));
+    CKI(check_tensor(Lr, SSDK_HT_WKV_U, H, D, "wkv.u")); CKI(check_tensor(Lr, SSDK_HT_MIX_NORM, HD, 1, "mix.norm"));
+    CKI(check_tensor(Lr, SSDK_HT_MIX_OUT, W, HD, "mix.o"));
+    float* st = e->state + Lr.state_off;
+    float* h_prev = st + (size_t)H * D * D;
+    const T* mixes = (const T*)e->mixes;
+    CKI(L.go(ssdk::token_shift_kernel<T>, dim3(M), dim3(256), 0, (const T*)e->h, (const T*)Lr.t[SSDK_HT_WKV_MU].p,
+             (const float*)h_prev, e->slot_floats, (T*)e->mixes, rg, W, 5));
+    float* pr = e->p0;
+    float* pk = pr + (size_t)M * HD;
+    float* pv = pk + (size_t)M * HD;
+    float* pg = pv + (size_t)M * HD;
+    float* pw = pg + (size_t)M * HD;
+    const size_t ms = (size_t)M * W;
+    CKI(lin(mixes + 0 * ms, W, Lr.t[SSDK_HT_WKV_R].p, W, pr, HD, M, HD, W));
+    CKI(lin(mixes + 1 * ms, W, Lr.t[SSDK_HT_WKV_K].p, W, pk, HD, M, HD, W));
+    CKI(lin(mixes + 2 * ms, W, Lr.t[SSDK_HT_WKV_V].p, W, pv, HD, M, HD, W));
+    CKI(lin(mixes + 3 * ms, W, Lr.t[SSDK_HT_WKV_G].p, W, pg, HD, M, HD, W));
+    CKI(lin(mixes + 4 * ms, W, Lr.t[SSDK_HT_WKV_W1].p, W, e->p1, c.decay_rank, M, c.decay_rank, W));
+    const size_t nt = (size_t)M * c.decay_rank;
+    CKI(L.go(ssdk::tanh_rows_kernel<T>, dim3((unsigned)std::min<size_t>((nt + 255) / 256, 4096)), dim3(256), 0,
+             (const float*)e->p1, (T*)e->t0, nt));
+    CKI(lin(e->t0, c.decay_rank, Lr.t[SSDK_HT_WKV_W2].p, c.decay_rank, pw, HD, M, HD, c.decay_rank));
+    ssdk::WkvArgs a;
+    a.r = pr; a.k = pk; a.v = pv; a.zw = pw; a.ld = HD; a.w0 = Lr.t[SSDK_HT_WKV_W0].p; a.u = Lr.t[SSDK_HT_WKV_U].p;
+    a.o = e->p2; a.state = st; a.slot_stride = e->slot_floats; a.h = e->h; a.h_prev = h_prev; a.width = W; a.H = H; a.D = D;
+    const size_t smem = (size_t)(D * D + 5 * D) * 4;
+    CKI(L.go(ssdk::wkv_scan_kernel<T>, dim3(rg.n_seqs, H), dim3((D + 31) / 32 * 32), smem, a, rg));
+    CKI(L.go(ssdk::head_rmsnorm_gate_kernel<T, 0>, dim3(M, H), dim3(std::min(256, (D + 31) / 32 * 32)), 0, (const float*)e->p2,
+             (const float*)pg, HD, (const T*)Lr.t[SSDK_HT_MIX_NORM].p, (T*)e->t1, H, D, e->cfg.eps));
+    return lin(e->t1, HD, Lr.t[SSDK_HT_MIX_OUT].p, HD, e->mix_out, W, M, W, HD);
+  }
+
+  int mlstm(HybLayer& Lr) {
+    const ssdk_hyb_layer_cfg& c = Lr.c;
+    const int H = c.heads, D = c.dim, V = c.vdim, W = e->cfg.width;
+    const int N = 2 * H * D + 2 * H * V + 2 * H;
+    CKI(check_tensor(Lr, SSDK_HT_MLSTM_IN, N, W, "mlstm.in")); CKI(check_tensor(Lr, SSDK_HT_MLSTM_IB, H, 1, "mlstm.i.b"));
+    CKI(check_tensor(Lr, SSDK_HT_MLSTM_FB, H, 1, "mlstm.f.b")); CKI(check_tensor(Lr, SSDK_HT_MIX_NORM, H * V, 1, "mix.norm"));
+    CKI(check_tensor(Lr, SSDK_HT_MIX_OUT, W, H * V, "mix.o"));
+    CKI(lin(e->h, W, Lr.t[SSDK_HT_MLSTM_IN].p, W, e->p0, N, M, N, W));
+    ssdk::MlstmArgs a;
+    a.q = e->p0; a.k = a.q + H * D; a.v = a.k + H * D;
+    const float* g = a.v + H * V;
+    a.ig = g + H * V; a.fg = a.ig + H; a.ld = N;
+    a.ib = Lr.t[SSDK_HT_MLSTM_IB].p; a.fb = Lr.t[SSDK_HT_MLSTM_FB].p; a.o = e->p2;
+    float* st = e->state + Lr.state_off;
+    a.S = st; a.n = st + (size_t)H * D * V; a.m = a.n + (size_t)H * D; a.slot_stride = e->slot_floats;
+    a.H = H; a.D = D; a.V = V; a.cap = c.gate_cap; a.q_scale = 1.0f / sqrtf((float)D);
+    const size_t smem = (size_t)(D * V + 3 * D) * 4;
+    CKI(L.go(ssdk::mlstm_scan_kernel<T>, dim3(rg.n_seqs, H), dim3((std::max(D, V) + 31) / 32 * 32), smem, a, rg));
+    CKI(L.go(ssdk::head_rmsnorm_gate_kernel<T, 1>, dim3(M, H), dim3(std::min(256, (V + 31) / 32 * 32)), 0, (const float*)e->p2, g, N,
+             (const T*)Lr.t[SSDK_HT_MIX_NORM].p, (T*)e->t1, H, V, e->cfg.eps));
+    return lin(e->t1, H * V, Lr.t[SSDK_HT_MIX_OUT].p, H * V, e->mix_out, W, M, W, H * V);
+  }
+
+  int latent(HybLayer& Lr) {
+    const ssdk_hyb_layer_cfg& c = Lr.c;
+    const int H = c.heads, D = c.dim, V = c.vdim, R = c.rot_dim, KR = c.kv_rank, QR = c.q_rank, W = e->cfg.width;
+    const int Nd = QR + KR + R;
+    CKI(check_tensor(Lr, SSDK_HT_LAT_DOWN, Nd, W, "latent.down")); CKI(check_tensor(Lr, SSDK_HT_LAT_QNORM, QR, 1, "dq.norm"));
+    CKI(check_tensor(Lr, SSDK_HT_LAT_KVNORM, KR, 1, "dkv.norm")); CKI(check_tensor(Lr, SSDK_HT_LAT_UQ, (int64_t)H * (D + R), QR, "uq"));
+    CKI(check_tensor(Lr, SSDK_HT_LAT_UKT, (int64_t)H * KR, D, "uk^T")); CKI(check_tensor(Lr, SSDK_HT_LAT_UV, (int64_t)H * V, KR, "uv"));
+    CKI(check_tensor(Lr, SSDK_HT_LAT_SINK, H, 1, "sink")); CKI(check_tensor(Lr, SSDK_HT_MIX_OUT, W, (int64_t)H * V, "mix.o"));
+    if (!e->cache) return fail("hybrid: latent cache not bound");
+    uint8_t* pool = e->cache + (size_t)e->num_blocks * e->cfg.block_size * Lr.cache_rows_before * e->esz;
+    CKI(lin(e->h, W, Lr.t[SSDK_HT_LAT_DOWN].p, W, e->p0, Nd, M, Nd, W));
+    ssdk::LatentPrepArgs pa;
+    pa.z = e->p0; pa.ldz = Nd; pa.qn_w = Lr.t[SSDK_HT_LAT_QNORM].p; pa.kvn_w = Lr.t[SSDK_HT_LAT_KVNORM].p; pa.cq = e->t0;
+    pa.cache = pool; pa.inv_freq = Lr.inv_freq; pa.q_rank = QR; pa.kv_rank = KR; pa.rot_dim = R; pa.rot_dims = c.rot_dims;
+    pa.eps = e->cfg.eps;
+    CKI(L.go(ssdk::latent_prep_kernel<T>, dim3(M), dim3(128), 0, pa, rg));
+    CKI(lin(e->t0, QR, Lr.t[SSDK_HT_LAT_UQ].p, QR, e->p1, H * (D + R), M, H * (D + R), QR));
+    CKI(L.go(ssdk::latent_q_kernel<T>, dim3(M, H), dim3(64), 0, (const float*)e->p1, (T*)e->t1, e->p2, (const float*)Lr.inv_freq, rg,
+             H, D, R, c.rot_dims));
+    // absorption: qlat[m, h, :] = W_uk,h^T qn[m, h, :]
+    CKI(lin(e->t1, H * D, Lr.t[SSDK_HT_LAT_UKT].p, D, e->p3, H * KR, M, KR, D, false, H, D, (long long)KR * D, KR));
+    ssdk::LatentAttnArgs aa;
+    aa.qlat = e->p3; aa.qr = e->p2; aa.cache = pool; aa.sink = Lr.t[SSDK_HT_LAT_SINK].p; aa.out = e->t0;
+    aa.H = H; aa.kv_rank = KR; aa.R = R; aa.scale = c.attn_scale;
+    const int Wd = KR + R, Wp = Wd | 1;
+    int hg = std::min(H, 16);
+    auto smem_of = [&](int g) { return (size_t)(g * Wd + ssdk::kLatKC * Wp + g * KR + g * ssdk::kLatKC + 3 * g) * 4; };
+    while (hg > 1 && smem_of(hg) > 200 * 1024) hg = (hg + 1) / 2;
+    if (smem_of(hg) > 200 * 1024) return fail("latent attention: row width %d too large for shared memory", Wd);
+    aa.hg = hg;
+    CKI(L.go(ssdk::latent_attn_kernel<T>, dim3(M, (H + hg - 1) / hg), dim3(ssdk::kLatThreads), smem_of(hg), aa, rg));
+    // per-head value projection of the latent output, rounded to T for the output projection
+    CKI(lin(e->t0, H * KR, Lr.t[SSDK_HT_LAT_UV].p, KR, e->t1, H * V, M, V, KR, true, H, KR, (long long)V * KR, V));
+    return lin(e->t1, H * V, Lr.t[SSDK_HT_MIX_OUT].p, H * V, e->mix_out, W, M, W, H * V);
+  }
+
+  int moe(HybLayer& Lr) {
+    const ssdk_hyb_layer_cfg& c = Lr.c;
+    const int W = e->cfg.width, E = c.experts, ff = c.ff, top = c.top, A = M * top;
+    CKI(check_tensor(Lr, SSDK_HT_ROUTER, E, W, "router")); CKI(check_tensor(Lr, SSDK_HT_EXPERT_IN, (int64_t)E * 2 * ff, W, "experts.in"));
+    CKI(check_tensor(Lr, SSDK_HT_EXPERT_OUT, (int64_t)E * W, ff, "experts.out"));
+    CKI(lin(e->h, W, Lr.t[SSDK_HT_ROUTER].p, W, e->rz, E, M, E, W));
+    ssdk::RouterArgs ra;
+    ra.z = e->rz; ra.sel = e->sel; ra.wts = e->wts; ra.M = M; ra.E = E; ra.top = top; ra.groups = c.groups; ra.keep = c.keep;
+    ra.route_scale = c.route_scale;
+    CKI(L.go(ssdk::group_topk_router_kernel, dim3((M + ssdk::kRouterWarps - 1) / ssdk::kRouterWarps), dim3(ssdk::kRouterWarps * 32), 0, ra));
+    ssdk::PlanArgs pa;
+    pa.sel = e->sel; pa.apos = e->apos; pa.arow = e->arow; pa.tile_expert = e->tile_expert; pa.tile_row0 = e->tile_row0;
+    pa.tile_rows = e->tile_rows; pa.n_tiles = e->n_tiles; pa.n_rows = e->n_rows; pa.A = A; pa.E = E; pa.top = top; pa.tile = ssdk::kLinBM;
+    CKI(L.go(ssdk::expert_plan_kernel, dim3(1), dim3(1024), 0, pa));
+    ssdk::LinearArgs a = {};
+    a.A = e->h; a.W = Lr.t[SSDK_HT_EXPERT_IN].p; a.C = e->eg; a.M = A; a.N = 2 * ff; a.K = W; a.lda = W; a.ldw = W; a.ldc = 2 * ff;
+    a.a_rows = e->arow; a.tile_expert = e->tile_expert; a.tile_row0 = e->tile_row0; a.tile_rows = e->tile_rows; a.n_tiles = e->n_tiles;
+    a.sW_expert = (long long)2 * ff * W;
+    CKI(lin_args<float>(a, A, 1));
+    CKI(L.go(ssdk::clamped_glu_kernel<T>, dim3(A), dim3(128), 0, (const float*)e->eg, 2 * ff, (T*)e->ey, ff, c.limit, (const int*)nullptr));
+    a.A = e->ey; a.W = Lr.t[SSDK_HT_EXPERT_OUT].p; a.C = e->eo; a.N = W; a.K = ff; a.lda = ff; a.ldw = ff; a.ldc = W; a.a_rows = nullptr;
+    a.sW_expert = (long long)W * ff;
+    CKI(lin_args<float>(a, A, 1));
+    if (c.shared_ff > 0) {
+      const int sff = c.shared_ff, Ns = 2 * sff + 1;
+      CKI(check_tensor(Lr, SSDK_HT_SHARED_IN, Ns, W, "shared.in")); CKI(check_tensor(Lr, SSDK_HT_SHARED_OUT, W, sff, "shared.out"));
+      CKI(lin(e->h, W, Lr.t[SSDK_HT_SHARED_IN].p, W, e->sz, Ns, M, Ns, W));
+      CKI(L.go(ssdk::clamped_glu_kernel<T>, dim3(M), dim3(128), 0, (const float*)e->sz, Ns, (T*)e->sy, sff, c.shared_limit, (const int*)nullptr));
+      CKI(lin(e->sy, sff, Lr.t[SSDK_HT_SHARED_OUT].p, sff, e->so, W, M, W, sff));
+    }
+    return 0;
+  }
+
+  int layer(HybLayer& Lr, int li) {
+    const int W = e->cfg.width;
+    CKI(check_tensor(Lr, SSDK_HT_NORM, W, 1, "norm1")); CKI(check_tensor(Lr, SSDK_HT_LS_MIX, W, 1, "ls1"));
+    CKI(L.go(ssdk::unit_offset_rmsnorm_kernel<T>, dim3(M), dim3(256), 0, (const float*)e->x, (const T*)Lr.t[SSDK_HT_NORM].p, (T*)e->h,
+             (const int*)nullptr, W, e->cfg.eps));
+    if (Lr.c.mixer == SSDK_MIX_WKV) CKI(wkv(Lr));
+    else if (Lr.c.mixer == SSDK_MIX_MLSTM) CKI(mlstm(Lr));
+    else CKI(latent(Lr));
+    ssdk::CombineArgs ca = {};
+    ca.x = e->x; ca.mix = e->mix_out; ca.ls1 = Lr.t[SSDK_HT_LS_MIX].p; ca.width = W;
+    if (Lr.c.mlp == SSDK_MLP_MOE) {
+      CKI(check_tensor(Lr, SSDK_HT_LS_MLP, W, 1, "ls2"));
+      CKI(moe(Lr));
+      ca.ls2 = Lr.t[SSDK_HT_LS_MLP].p; ca.routed = e->eo; ca.apos = e->apos; ca.wts = e->wts; ca.top = Lr.c.top;
+      if (Lr.c.shared_ff > 0) { ca.shared = e->so; ca.sg = e->sz + 2 * Lr.c.shared_ff; ca.ld_sg = 2 * Lr.c.shared_ff + 1; }
+    }
+    return L.go(ssdk::block_combine_kernel<T>, dim3(M), dim3(256), 0, ca);
+  }
+};
+
+static int hyb_smem_attrs(ssdk_hyb_engine* e) {
+  if (e->smem_attr_done) return 0;
+  const int big = 200 * 1024;
+  CK(cudaFuncSetAttribute(ssdk::wkv_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+  CK(cudaFuncSetAttribute(ssdk::wkv_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+  CK(cudaFuncSetAttribute(ssdk::mlstm_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+  CK(cudaFuncSetAttribute(ssdk::mlstm_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+  CK(cudaFuncSetAttribute(ssdk::latent_attn_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+  CK(cudaFuncSetAttribute(ssdk::latent_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+  e->smem_attr_done = true;
+  return 0;
+}
+
+template <typename T>
+static int hyb_forward_t(ssdk_hyb_engine* e, int n_seqs, int M, const int32_t* ids, const int32_t* cu, const int32_t* pos0,
+                         const int32_t* slot, const int32_t* tables, int n_want, const int32_t* want_rows, float* logits_host,
+                         const float* temps, uint64_t seed, uint64_t step_id, int64_t* out_tokens, float* residual_host,
+                         cudaStream_t st) {
+  const ssdk_hyb_cfg& g = e->cfg;
+  CKI(hyb_smem_attrs(e));
+  // stage the step's integers: ids | tok_seq | cu | pos0 | slot | tables | want_rows
+  int* hm = e->h_meta;
+  int* d = e->meta;
+  size_t o = 0;
+  const size_t o_ids = o; memcpy(hm + o, ids, (size_t)M * 4); o += M;
+  const size_t o_seq = o;
+  for (int s = 0; s < n_seqs; ++s)
+    for (int r = cu[s]; r < cu[s + 1]; ++r) hm[o_seq + r] = s;
+  o += M;
+  const size_t o_cu = o; memcpy(hm + o, cu, (size_t)(n_seqs + 1) * 4); o += n_seqs + 1;
+  const size_t o_pos = o; memcpy(hm + o, pos0, (size_t)n_seqs * 4); o += n_seqs;
+  const size_t o_slot = o; memcpy(hm + o, slot, (size_t)n_seqs * 4); o += n_seqs;
+  const size_t o_tab = o; memcpy(hm + o, tables, (size_t)n_seqs * g.max_blocks_per_seq * 4); o += (size_t)n_seqs * g.max_blocks_per_seq;
+  const size_t o_want = o; if (n_want) memcpy(hm + o, want_rows, (size_t)n_want * 4); o += n_want;
+  CK(cudaMemcpyAsync(d, hm, o * 4, cudaMemcpyHostToDevice, st));
+  HybRun<T> run;
+  run.e = e; run.L.st = st; run.L.pdl = false; run.M = M;
+  run.rg.cu = d + o_cu; run.rg.pos0 = d + o_pos; run.rg.slot = d + o_slot; run.rg.tok_seq = d + o_seq; run.rg.tables = d + o_tab;
+  run.rg.n_seqs = n_seqs; run.rg.M = M; run.rg.max_blocks = g.max_blocks_per_seq; run.rg.block_size = g.block_size;
+  CKI(run.L.go(ssdk::embed_rows_kernel<T>, dim3(M), dim3(128), 0, (const int*)(d + o_ids), (const T*)e->embed.p, e->x, g.width, g.vocab));
+  for (int li = 0; li < g.n_layers; ++li) {
+    CKI(run.layer(e->layers[li], li));
+    if (residual_host)
+      CK(cudaMemcpyAsync(residual_host + (size_t)li * M * g.width, e->x, (size_t)M * g.width * 4, cudaMemcpyDeviceToHost, st));
+  }
+  if (n_want > 0) {
+    CKI(run.L.go(ssdk::unit_offset_rmsnorm_kernel<T>, dim3(n_want), dim3(256), 0, (const float*)e->x, (const T*)e->final_norm.p, (T*)e->hn,
+                 (const int*)(d + o_want), g.width, g.eps));
+    CKI(run.lin(e->hn, g.width, e->head.p, g.width, e->logits, g.vocab, n_want, g.vocab, g.width));
+    if (logits_host) CK(cudaMemcpyAsync(logits_host, e->logits, (size_t)n_want * g.vocab * 4, cudaMemcpyDeviceToHost, st));
+    if (temps && out_tokens) {
+      const size_t n = (size_t)n_want * g.vocab;
+      CKI(run.L.go(ssdk::f32_to_bf16_kernel, dim3((unsigned)std::min<size_t>((n + 255) / 256, 8192)), dim3(256), 0, (const float*)e->logits,
+                   e->logits16, n));
+      CK(cudaMemcpyAsync(e->temps, temps, (size_t)n_want * 4, cudaMemcpyHostToDevice, st));
+      void* scr = nullptr;
+      CKI(op_scratch(&scr, st));
+      for (int r0 = 0; r0 < n_want; r0 += 256) {
+        const int nb = std::min(256, n_want - r0);
+        SampleParams sp;
+        sp.logits = e->logits16 + (size_t)r0 * g.vocab; sp.ld = g.vocab; sp.temps = e->temps + r0; sp.V = g.vocab; sp.seed = seed;
+        sp.call_id = step_id; sp.out = e->tokens + r0; sp.out_stride = 1; sp.counters = (unsigned*)scr;
+        sp.partial = (ArgMax*)((uint8_t*)scr + 4096); sp.dyn = nullptr; sp.sub = 0;
+        CKI(run.L.go(sample_kernel, dim3(kSampleChunks, nb), dim3(256), 0, sp));
+      }
+      CK(cudaMemcpyAsync(out_tokens, e->tokens, (size_t)n_want * 8, cudaMemcpyDeviceToHost, st));
+    }
+  }
+  e->launches += run.L.count;
+  CK(cudaStreamSynchronize(st));
+  return 0;
+}
+
+extern "C" {
+
+int ssdk_hyb_create(const ssdk_hyb_cfg* cfg, const ssdk_hyb_layer_cfg* layers, ssdk_hyb_handle* out) {
+  if (!cfg || !layers || !out) return fail("ssdk_hyb_create: null argument");
+  if (cfg->width < 1 || cfg->vocab < 1 || cfg->n_layers < 1) return fail("ssdk_hyb_create: bad sizes");
+  if (cfg->dtype != SSDK_DT_F32 && cfg->dtype != SSDK_DT_BF16) return fail("ssdk_hyb_create: unknown dtype %d", cfg->dtype);
+  if (cfg->max_tokens < 1 || cfg->max_seqs < 1 || cfg->max_logit_rows < 1 || cfg->block_size < 1 || cfg->max_blocks_per_seq < 1)
+    return fail("ssdk_hyb_create: bad runtime limits");
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev < 1) return fail("ssdk_hyb_create: no CUDA device (there is no CPU path)");
+  auto* e = new ssdk_hyb_engine();
+  e->cfg = *cfg;
+  e->esz = cfg->dtype == SSDK_DT_BF16 ? 2 : 4;
+  e->layers.resize(cfg->n_layers);
+  for (int i = 0; i < cfg->n_layers; ++i) e->layers[i].c = layers[i];
+  if (hyb_derive(e) != 0) { delete e; return -1; }
+  for (auto& L : e->layers) {
+    if (L.c.mixer != SSDK_MIX_LATENT_ATTN || L.c.rot_dims < 2) continue;
+    const int half = L.c.rot_dims / 2;
+    std::vector<float> f(half);
+    for (int i = 0; i < half; ++i) f[i] = (float)pow((double)L.c.rot_base, -2.0 * i / (double)L.c.rot_dims);
+    if (cudaMalloc(&L.inv_freq, half * 4) != cudaSuccess ||
+        cudaMemcpy(L.inv_freq, f.data(), half * 4, cudaMemcpyHostToDevice) != cudaSuccess) {
+      delete e;
+      return fail("ssdk_hyb_create: could not place the rotation frequencies on the device");
+    }
+  }
+  e->ws_bytes = hyb_carve(e, nullptr);
+  if (cudaMallocHost(&e->h_meta, e->meta_ints * 4) != cudaSuccess) { delete e; return fail("ssdk_hyb_create: pinned staging allocation failed"); }
+  *out = e;
+  return 0;
+}
+
+int ssdk_hyb_destroy(ssdk_hyb_handle e) {
+  if (!e) return 0;
+  for (auto& L : e->layers)
+    if (L.inv_freq) cudaFree(L.inv_freq);
+  if (e->h_meta) cudaFreeHost(e->h_meta);
+  delete e;
+  return 0;
+}
+
+int ssdk_hyb_bind(ssdk_hyb_handle e, int layer, int tensor, const void* dev_ptr, int64_t rows, int64_t cols) {
+  if (!e || !dev_ptr) return fail("ssdk_hyb_bind: null argument");
+  if (tensor < 0 || tensor >= SSDK_HT_COUNT) return fail("ssdk_hyb_bind: unknown tensor %d", tensor);
+  HybTensor t;
+  t.p = dev_ptr; t.rows = rows; t.cols = cols;
+  if (tensor == SSDK_HT_EMBED || tensor == SSDK_HT_HEAD || tensor == SSDK_HT_FINAL_NORM) {
+    const int64_t want = tensor == SSDK_HT_FINAL_NORM ? e->cfg.width : (int64_t)e->cfg.vocab * e->cfg.width;
+    if (rows * cols != want) return fail("ssdk_hyb_bind: tensor %d has %lld elements, expected %lld", tensor, (long long)(rows * cols), (long long)want);
+    (tensor == SSDK_HT_EMBED ? e->embed : tensor == SSDK_HT_HEAD ? e->head : e->final_norm) = t;
+    return 0;
+  }
+  if (layer < 0 || layer >= e->cfg.n_layers) return fail("ssdk_hyb_bind: layer %d out of range", layer);
+  e->layers[layer].t[tensor] = t;
+  return 0;
+}
+
+int64_t ssdk_hyb_cache_bytes(ssdk_hyb_handle e, int64_t num_blocks) {
+  if (!e) return -1;
+  return (int64_t)(num_blocks * e->cfg.block_size * e->cache_row_total * e->esz);
+}
+int64_t ssdk_hyb_state_bytes(ssdk_hyb_handle e, int64_t n_slots) {
+  if (!e) return -1;
+  return (int64_t)(n_slots * e->slot_floats * 4);
+}
+int64_t ssdk_hyb_workspace_bytes(ssdk_hyb_handle e) { return e ? e->ws_bytes : -1; }
+
+int ssdk_hyb_bind_pools(ssdk_hyb_handle e, void* cache, int64_t num_blocks, void* state, int64_t n_slots, void* workspace,
+                        int64_t workspace_bytes) {
+  if (!e) return fail("ssdk_hyb_bind_pools: null handle");
+  if (e->cache_row_total && (!cache || num_blocks < 1)) return fail("ssdk_hyb_bind_pools: the model has latent attention but no cache was given");
+  if (e->slot_floats && (!state || n_slots < 1)) return fail("ssdk_hyb_bind_pools: the model has recurrent layers but no state pool was given");
+  if (!workspace || workspace_bytes < e->ws_bytes) return fail("ssdk_hyb_bind_pools: workspace too small");
+  if (((uintptr_t)workspace & 255) || ((uintptr_t)cache & 15) || ((uintptr_t)state & 15)) return fail("ssdk_hyb_bind_pools: misaligned pool");
+  e->cache = (uint8_t*)cache; e->num_blocks = num_blocks; e->state = (float*)state; e->n_slots = n_slots;
+  hyb_carve(e, (uint8_t*)workspace);
+  return 0;
+}
+
+int ssdk_hyb_forward(ssdk_hyb_handle e, int n_seqs, int n_tokens, const int32_t* ids, const int32_t* cu, const int32_t* pos0,
+                     const int32_t* slot, const int32_t* tables, int n_want, const int32_t* want_rows, float* logits_host,
+                     const float* temps, uint64_t seed, uint64_t step_id, int64_t* out_tokens, float* residual_host, void* stream) {
+  if (!e || !e->x) return fail("ssdk_hyb_forward: pools not bound");
+  const ssdk_hyb_cfg& g = e->cfg;
+  if (n_seqs < 1 || n_seqs > g.max_seqs) return fail("ssdk_hyb_forward: %d sequences (1..%d)", n_seqs, g.max_seqs);
+  if (n_tokens < 1 || n_tokens > g.max_tokens) return fail("ssdk_hyb_forward: %d rows (1..%d)", n_tokens, g.max_tokens);
+  if (n_want < 0 || n_want > g.max_logit_rows) return fail("ssdk_hyb_forward: %d logit rows (0..%d)", n_want, g.max_logit_rows);
+  if (!e->embed.p || !e->head.p || !e->final_norm.p) return fail("ssdk_hyb_forward: embedding / head / final norm not bound");
+  if (cu[0] != 0 || cu[n_seqs] != n_tokens) return fail("ssdk_hyb_forward: row offsets do not cover the batch");
+  for (int s = 0; s < n_seqs; ++s) {
+    if (cu[s + 1] <= cu[s]) return fail("ssdk_hyb_forward: sequence %d brings no rows", s);
+    if (pos0[s] < 0) return fail("ssdk_hyb_forward: negative position");
+    if (e->slot_floats && (slot[s] < 0 || slot[s] >= e->n_slots)) return fail("ssdk_hyb_forward: state slot %d out of range", slot[s]);
+    for (int s2 = 0; s2 < s; ++s2)
+      if (e->slot_floats && slot[s2] == slot[s]) return fail("ssdk_hyb_forward: two sequences share state slot %d", slot[s]);
+    if (e->cache_row_total) {
+      const int last = pos0[s] + (cu[s + 1] - cu[s]) - 1;
+      if (last / g.block_size >= g.max_blocks_per_seq) return fail("ssdk_hyb_forward: sequence %d outgrows its page table", s);
+      for (int b = 0; b <= last / g.block_size; ++b) {
+        const int pg = tables[(size_t)s * g.max_blocks_per_seq + b];
+        if (pg < 0 || pg >= e->num_blocks) return fail("ssdk_hyb_forward: page %d of sequence %d out of range", pg, s);
+      }
+    }
+  }
+  for (int i = 0; i < n_want; ++i)
+    if (want_rows[i] < 0 || want_rows[i] >= n_tokens) return fail("ssdk_hyb_forward: logit row out of range");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (g.dtype == SSDK_DT_BF16)
+    return hyb_forward_t<bf16>(e, n_seqs, n_tokens, ids, cu, pos0, slot, tables, n_want, want_rows, logits_host, temps, seed, step_id,
+                               out_tokens, residual_host, st);
+  return hyb_forward_t<float>(e, n_seqs, n_tokens, ids, cu, pos0, slot, tables, n_want, want_rows, logits_host, temps, seed, step_id,
+                              out_tokens, residual_host, st);
+}
+
+int64_t ssdk_hyb_launch_count(ssdk_hyb_handle e) { return e ? e->launches : -1; }
+
+}  // extern "C"

@@ -1,0 +1,119 @@
+// linear.cuh — shape-generic linear layers for the layered (hybrid) models: C[M,N] = A[M,K] · W[N,K]^T with fp32
+// accumulation for ANY M, N, K (head sizes such as 40 or 48 have no 64-column TMA box), in two storage types:
+//   T = bf16 : operands bf16, products exact in fp32, fp32 accumulate (the rounding contract of a tensor-core GEMM);
+//              tile products on mma.sync.m16n8k16 when K is a multiple of 16, CUDA-core FMA otherwise
+//   T = float: true fp32 FMA (no TF32), used by the exact mode
+// Three addressing modes share one kernel: dense, batched (blockIdx.z walks per-head slices by strides) and grouped
+// (a tile list made on the device by the router maps tile -> expert / first row / row count; the rows of A may be
+// gathered through an index).  The accumulation order of an output element depends on K alone, never on M or on which
+// other rows share the tile, so a token's result is independent of the batch it ran in.
+// Large aligned bf16 products take the tcgen05 path of gemm.cuh instead (see enqueue_linear in hybrid_engine.cuh).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace ssdk {
+
+template <typename T> SSDK_DEVINL float ld_f(const T* p);
+template <> SSDK_DEVINL float ld_f<float>(const float* p) { return *p; }
+template <> SSDK_DEVINL float ld_f<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> SSDK_DEVINL void st_f(T* p, float v);
+template <> SSDK_DEVINL void st_f<float>(float* p, float v) { *p = v; }
+template <> SSDK_DEVINL void st_f<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+struct LinearArgs {
+  const void* A;   // [*, lda]  storage type T
+  const void* W;   // [N, ldw]  storage type T
+  void* C;         // [*, ldc]  fp32 or T
+  int M, N, K;
+  int lda, ldw, ldc;
+  long long sA, sW, sC;    // element strides per blockIdx.z (batched mode)
+  const int* a_rows;       // optional gather: logical row r of A lives at row a_rows[r]
+  // grouped mode (tile_expert != nullptr): blockIdx.y indexes the tile list
+  const int* tile_expert;
+  const int* tile_row0;
+  const int* tile_rows;
+  const int* n_tiles;
+  long long sW_expert;     // elements between two experts' matrices
+};
+
+constexpr int kLinBM = 64, kLinBN = 64, kLinBK = 16, kLinThreads = 256;
+
+// CUDA-core tile: 64 x 64 outputs per CTA, 4 x 4 per thread, operands staged as fp32 in shared memory.
+template <typename T, typename OutT>
+__global__ void __launch_bounds__(kLinThreads) linear_kernel(const LinearArgs p) {
+  __shared__ float As[kLinBK][kLinBM + 4];
+  __shared__ float Ws[kLinBK][kLinBN + 4];
+  int row0, nrows;
+  const T* W = (const T*)p.W + (long long)blockIdx.z * p.sW;
+  const T* A = (const T*)p.A + (long long)blockIdx.z * p.sA;
+  OutT* C = (OutT*)p.C + (long long)blockIdx.z * p.sC;
+  if (p.tile_expert) {
+    if ((int)blockIdx.y >= *p.n_tiles) return;
+    W += (long long)p.tile_expert[blockIdx.y] * p.sW_expert;
+    row0 = p.tile_row0[blockIdx.y];
+    nrows = p.tile_rows[blockIdx.y];
+  } else {
+    row0 = blockIdx.y * kLinBM;
+    nrows = min(kLinBM, p.M - row0);
+    if (nrows <= 0) return;
+  }
+  const int col0 = blockIdx.x * kLinBN;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  // each thread stages 4 elements of A and 4 of W per k-step: element e -> (row e / 16, k e % 16)
+  long long a_off[4], w_off[4];
+  bool a_ok[4], w_ok[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int e = tid + i * kLinThreads, r = e >> 4;
+    a_ok[i] = r < nrows;
+    int ar = row0 + r;
+    if (a_ok[i] && p.a_rows) ar = p.a_rows[ar];
+    a_off[i] = (long long)ar * p.lda;
+    w_ok[i] = col0 + r < p.N;
+    w_off[i] = (long long)(col0 + r) * p.ldw;
+  }
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < p.K; k0 += kLinBK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int e = tid + i * kLinThreads, r = e >> 4, kk = e & 15;
+      const bool kin = k0 + kk < p.K;
+      As[kk][r] = (a_ok[i] && kin) ? ld_f<T>(A + a_off[i] + k0 + kk) : 0.f;
+      Ws[kk][r] = (w_ok[i] && kin) ? ld_f<T>(W + w_off[i] + k0 + kk) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kLinBK; ++kk) {
+      float a[4], w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = ty * 4 + i;
+    if (r >= nrows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = col0 + tx * 4 + j;
+      if (c < p.N) st_f<OutT>(C + (long long)(row0 + r) * p.ldc + c, acc[i][j]);
+    }
+  }
+}
+
+}  // namespace ssdk

@@ -20,10 +20,13 @@ class _Page:
 
 class BlockManager:
     def __init__(self, num_blocks: int, block_size: int, is_draft: bool = False, speculate_k: int = -1,
-                 max_model_len: int = -1, verbose: bool = False):
+                 max_model_len: int = -1, verbose: bool = False,
+                 prefix_reuse: bool = True):
         if num_blocks <= 0:
             raise ValueError("KV cache has no blocks")
         self.block_size, self.is_draft, self.max_model_len = block_size, is_draft, max_model_len
+        # False for models with recurrent layers: a cached page is of no use without the state that went with it
+        self.prefix_reuse = prefix_reuse
         self.blocks = [_Page(i) for i in range(num_blocks)]
         self.free_block_ids: deque[int] = deque(range(num_blocks))
         self.used_block_ids: set[int] = set()
@@ -59,6 +62,8 @@ class BlockManager:
 
     def seal(self, seq, index: int) -> None:
         """A block of `seq` became full: record its chained hash so later prompts can reuse it."""
+        if not self.prefix_reuse:
+            return
         table = self._table(seq)
         tokens = seq.block(index)
         prev = self.blocks[table[index - 1]].digest if index > 0 else -1
@@ -77,7 +82,7 @@ class BlockManager:
         digest, missed = -1, False
         for i in range(seq.num_blocks):
             tokens = seq.block(i)
-            full = len(tokens) == self.block_size
+            full = len(tokens) == self.block_size and self.prefix_reuse
             digest = self.compute_hash(tokens, digest) if full else -1
             pid = self.hash_to_block_id.get(digest, -1)
             if pid == -1 or self.blocks[pid].tokens != tokens:

@@ -13,7 +13,7 @@ from .sequence import Sequence, SequenceStatus
 
 
 class Scheduler:
-    def __init__(self, config, draft_cfg=None):
+    def __init__(self, config, draft_cfg=None, state_manager=None, prefix_reuse: bool = True):
         self.max_num_seqs = config.max_num_seqs
         self.max_num_batched_tokens = config.max_num_batched_tokens
         self.max_model_len = config.max_model_len
@@ -22,7 +22,9 @@ class Scheduler:
         self.K = config.speculate_k
         self.block_size = config.kvcache_block_size
         self.block_manager = BlockManager(config.num_kvcache_blocks, self.block_size, is_draft=False,
-                                          max_model_len=self.max_model_len)
+                                          max_model_len=self.max_model_len, prefix_reuse=prefix_reuse)
+        # hybrid models: one recurrent-state slot per running sequence (engine/state_manager.py)
+        self.state_manager = state_manager
         self.draft_block_manager = None
         if self.speculate:
             nb = getattr(draft_cfg, "num_kvcache_blocks", config.num_kvcache_blocks)
@@ -50,8 +52,12 @@ class Scheduler:
             need = len(seq) - seq.num_cached_tokens
             if need > budget or not all(m.can_allocate(seq) for m in self._managers()):
                 break
+            if self.state_manager is not None and not self.state_manager.can_allocate():
+                break
             for m in self._managers():
                 m.allocate(seq)
+            if self.state_manager is not None:
+                self.state_manager.allocate(seq)
             budget -= need
             seq.status = SequenceStatus.RUNNING
             self.running.append(self.waiting.popleft())
@@ -88,8 +94,7 @@ class Scheduler:
         """Out of KV blocks: drop the sequence's cache and re-prefill it later (completions become prompt)."""
         seq.status = SequenceStatus.WAITING
         seq.recovery_token_id = None
-        for m in self._managers():
-            m.deallocate(seq)
+        self._release(seq)
         seq.num_prompt_tokens = seq.num_tokens
         seq.last_spec_step_accepted_len = -1
         self.waiting.appendleft(seq)
@@ -141,14 +146,46 @@ class Scheduler:
             if finished:
                 self._finish(seq)
 
-    def _retire(self, seq: Sequence) -> None:
-        seq.status = SequenceStatus.FINISHED
+    def _release(self, seq: Sequence) -> None:
         for m in self._managers():
             m.deallocate(seq)
+        if self.state_manager is not None:
+            self.state_manager.free(seq)
+
+    # -------------------------------------------------------------------- externally planned steps
+    def extend(self, seq: Sequence, tokens: list[int]) -> int:
+        """A caller that plans its own steps (trace replay, chunked prefill) brings the next `tokens` of `seq`: admit it
+        on its first portion (pages for what it holds + a state slot), grow its page table on later ones.  Returns the
+        position of the portion's first token.  Raises if the pools cannot hold it."""
+        if seq.status is not SequenceStatus.RUNNING:
+            if self.state_manager is not None and not self.state_manager.can_allocate():
+                raise RuntimeError("no free state slot")
+            pos0 = 0
+            seq.token_ids = list(tokens)
+            seq.num_prompt_tokens = len(seq.token_ids)
+            if not self.block_manager.can_allocate(seq):
+                raise RuntimeError("out of cache pages")
+            self.block_manager.allocate(seq)
+            if self.state_manager is not None:
+                self.state_manager.allocate(seq)
+            seq.status = SequenceStatus.RUNNING
+            self.running.append(seq)
+        else:
+            pos0 = seq.num_tokens
+            seq.token_ids.extend(tokens)
+            self.block_manager.may_append(seq, 0)
+        return pos0
+
+    def release(self, seq: Sequence) -> None:
+        """End of an externally planned sequence: pages and slot go back to the pools."""
+        self._finish(seq)
+
+    def _retire(self, seq: Sequence) -> None:
+        seq.status = SequenceStatus.FINISHED
+        self._release(seq)
         self.retired.append(seq)
 
     def _finish(self, seq: Sequence) -> None:
         seq.status = SequenceStatus.FINISHED
-        for m in self._managers():
-            m.deallocate(seq)
+        self._release(seq)
         self.running.remove(seq)

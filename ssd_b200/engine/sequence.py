@@ -31,6 +31,7 @@ class Sequence:
         self.num_draft_cached_tokens = 0
         self.block_table: list[int] = []
         self.draft_block_table: list[int] = []
+        self.state_slot = -1  # recurrent-state slot of a hybrid model (engine/state_manager.py)
         self.temperature = sp.temperature
         self.draft_temperature = sp.draft_temperature
         self.max_new_tokens = sp.max_new_tokens

@@ -1,0 +1,338 @@
+"""Layered ("hybrid") models: a program of layers, each one token mixer + an optional mixture-of-experts feed-forward
+in a parallel block.  The design served through this module is Pikavik (config.json `"architecture": "Pikavik"`): mLSTM,
+RWKV-style wkv and latent-attention mixers in any order.
+
+    HybridSpec     what config.json (and, for sizes it does not list, the checkpoint's tensor shapes) says
+    load_hybrid_weights   safetensors -> device tensors in the packed layout libssdk's ssdk_hyb_bind expects
+    HybridRunner   owner of the device state behind one ssdk_hyb handle (weights, paged latent cache, recurrent-state
+                   slots, workspace); `forward` runs one ragged batch — prompt portions beside single decode tokens
+
+PyTorch is plumbing only (allocation, host->device copies of weights); every FLOP runs in libssdk.  The reference has no
+model of this family, so nothing here cites it; the runner mirrors PairRunner's conventions (runner.py)."""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import os
+import struct
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from . import lib as L
+
+MIXERS = {"wkv": L.MIX_WKV, "mlstm": L.MIX_MLSTM, "latent_attention": L.MIX_LATENT_ATTN}
+
+
+@dataclass
+class LayerSpec:
+    mixer: str
+    heads: int
+    dim: int
+    vdim: int = 0
+    rot_dim: int = 0
+    rot_dims: int = 0
+    rot_base: float = 10000.0
+    kv_rank: int = 0
+    q_rank: int = 0
+    attn_scale: float = 1.0
+    gate_cap: float = 0.0
+    decay_rank: int = 0
+    # feed-forward (None = the layer has none)
+    mlp: str | None = None
+    experts: int = 0
+    top: int = 0
+    groups: int = 1
+    keep: int = 1
+    route_scale: float = 1.0
+    ff: int = 0
+    limit: float = 0.0
+    shared_ff: int = 0
+    shared_limit: float = 0.0
+
+    def cfg(self) -> L.HybLayerCfg:
+        return L.HybLayerCfg(MIXERS[self.mixer], self.heads, self.dim, self.vdim, self.rot_dim, self.rot_dims, self.kv_rank,
+                             self.q_rank, self.decay_rank, self.rot_base, self.attn_scale, self.gate_cap,
+                             L.MLP_MOE if self.mlp == "moe" else L.MLP_NONE, self.experts, self.top, self.groups, self.keep,
+                             self.ff, self.shared_ff, self.route_scale, self.limit, self.shared_limit)
+
+
+@dataclass
+class HybridSpec:
+    width: int
+    vocab: int
+    eps: float
+    layers: list[LayerSpec] = field(default_factory=list)
+    architecture: str = "Pikavik"
+
+    @property
+    def has_latent(self) -> bool:
+        return any(l.mixer == "latent_attention" for l in self.layers)
+
+    @property
+    def has_state(self) -> bool:
+        return any(l.mixer != "latent_attention" for l in self.layers)
+
+    @classmethod
+    def from_config(cls, cfg: dict, shapes: dict[str, list[int]] | None = None) -> "HybridSpec":
+        """cfg: the parsed config.json.  shapes: tensor name -> shape of the checkpoint, for the sizes that only a
+        tensor gives (the rank of the wkv decay bottleneck)."""
+        layers = []
+        for i, lc in enumerate(cfg["layers"]):
+            kind, m = lc["type"], lc["mixer"]
+            if kind not in MIXERS:
+                raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+            ls = LayerSpec(mixer=kind, heads=int(m["heads"]), dim=int(m["dim"]))
+            if kind == "wkv":
+                ls.vdim = ls.dim
+                if shapes is not None:
+                    ls.decay_rank = int(shapes[f"l{i}.mix.w1"][0])
+                else:
+                    ls.decay_rank = int(m.get("decay_rank", 0))
+                if ls.decay_rank < 1:
+                    raise ValueError(f"layer {i}: the decay bottleneck's rank is unknown")
+            elif kind == "mlstm":
+                ls.vdim, ls.gate_cap = int(m["vdim"]), float(m["gate_cap"])
+            else:
+                rot = m.get("rot") or {}
+                ls.vdim, ls.rot_dim = int(m["vdim"]), int(m["rot_dim"])
+                ls.rot_dims, ls.rot_base = int(rot.get("dims", ls.rot_dim)), float(rot.get("base", 10000.0))
+                ls.kv_rank, ls.q_rank, ls.attn_scale = int(m["kv_rank"]), int(m["q_rank"]), float(m["scale"])
+            mlp = lc.get("mlp")
+            if mlp:
+                if mlp.get("kind", "moe") != "moe":
+                    raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+                r, ex, sh = mlp["router"], mlp["expert"], mlp.get("shared")
+                g = r.get("groups") or {}
+                ls.mlp, ls.experts, ls.top = "moe", int(r["experts"]), int(r["top"])
+                ls.groups, ls.keep = int(g.get("count", 1)), int(g.get("keep", g.get("count", 1)))
+                ls.route_scale, ls.ff, ls.limit = float(r.get("scale", 1.0)), int(ex["ff"]), float(ex["limit"])
+                if sh:
+                    ls.shared_ff, ls.shared_limit = int(sh["ff"]), float(sh["limit"])
+            layers.append(ls)
+        return cls(width=int(cfg["width"]), vocab=int(cfg["vocab"]), eps=float(cfg["norm"]["eps"]), layers=layers,
+                   architecture=cfg.get("architecture", "Pikavik"))
+
+    @classmethod
+    def from_dir(cls, path: str) -> "HybridSpec":
+        with open(os.path.join(path, "config.json")) as f:
+            cfg = json.load(f)
+        return cls.from_config(cfg, safetensors_shapes(os.path.join(path, "model.safetensors")))
+
+
+def safetensors_header(path: str) -> tuple[dict, int]:
+    """(name -> {dtype, shape, data_offsets}, offset of the data section): 8-byte little-endian length, then JSON."""
+    with open(path, "rb") as f:
+        n = struct.unpack("<Q", f.read(8))[0]
+        header = json.loads(f.read(n))
+    header.pop("__metadata__", None)
+    return header, 8 + n
+
+
+def safetensors_shapes(path: str) -> dict[str, list[int]]:
+    return {k: v["shape"] for k, v in safetensors_header(path)[0].items()}
+
+
+_ST_DTYPES = {"BF16": torch.bfloat16, "F32": torch.float32, "F16": torch.float16, "I32": torch.int32, "I64": torch.int64,
+              "F64": torch.float64}
+
+
+def read_safetensors(path: str) -> dict[str, torch.Tensor]:
+    header, base = safetensors_header(path)
+    raw = np.fromfile(path, dtype=np.uint8)
+    out = {}
+    for name, info in header.items():
+        lo, hi = info["data_offsets"]
+        buf = torch.from_numpy(raw[base + lo:base + hi].copy())
+        out[name] = buf.view(_ST_DTYPES[info["dtype"]]).reshape(info["shape"])
+    return out
+
+
+def pack_hybrid_weights(spec: HybridSpec, raw: dict[str, torch.Tensor], dtype: torch.dtype, device) -> dict:
+    """Checkpoint tensors -> the packed per-layer tensors of ssdk_hyb_bind (include/ssdk.h, SSDK_HT_*): projections that
+    read the same input are stacked by output rows, per-expert matrices are stacked by expert, W_uk is transposed per
+    head for the query absorption."""
+    def t(name):
+        return raw[name].to(torch.float32)
+
+    def dev(x):
+        return x.to(dtype).contiguous().to(device)
+
+    w = {"EMBED": dev(t("embed")), "HEAD": dev(t("head")), "FINAL_NORM": dev(t("final.norm")), "layers": []}
+    for i, ls in enumerate(spec.layers):
+        p, mx = f"l{i}.", f"l{i}.mix."
+        lw = {"NORM": dev(t(p + "norm1")), "LS_MIX": dev(t(p + "ls1")), "MIX_OUT": dev(t(mx + "o"))}
+        if ls.mixer == "wkv":
+            lw["WKV_MU"] = dev(torch.stack([t(mx + "mu." + s) for s in "rkvgw"]))
+            for s in "rkvg":
+                lw["WKV_" + s.upper()] = dev(t(mx + s))
+            lw["WKV_W1"], lw["WKV_W2"], lw["WKV_W0"] = dev(t(mx + "w1")), dev(t(mx + "w2")), dev(t(mx + "w0"))
+            lw["WKV_U"], lw["MIX_NORM"] = dev(t(mx + "u")), dev(t(mx + "norm"))
+        elif ls.mixer == "mlstm":
+            lw["MLSTM_IN"] = dev(torch.cat([t(mx + s) for s in ("q", "k", "v", "g", "i", "f")]))
+            lw["MLSTM_IB"], lw["MLSTM_FB"], lw["MIX_NORM"] = dev(t(mx + "i.b")), dev(t(mx + "f.b")), dev(t(mx + "norm"))
+        else:
+            lw["LAT_DOWN"] = dev(torch.cat([t(mx + "dq"), t(mx + "dkv")]))
+            lw["LAT_QNORM"], lw["LAT_KVNORM"] = dev(t(mx + "dq.norm")), dev(t(mx + "dkv.norm"))
+            lw["LAT_UQ"], lw["LAT_UV"], lw["LAT_SINK"] = dev(t(mx + "uq")), dev(t(mx + "uv")), dev(t(mx + "sink"))
+            lw["LAT_UKT"] = dev(t(mx + "uk").view(ls.heads, ls.dim, ls.kv_rank).transpose(1, 2))
+        if ls.mlp == "moe":
+            q = p + "mlp."
+            lw["LS_MLP"], lw["ROUTER"] = dev(t(p + "ls2")), dev(t(q + "router"))
+            lw["EXPERT_IN"] = dev(torch.stack([torch.cat([t(f"{q}e{e}.gate"), t(f"{q}e{e}.up")]) for e in range(ls.experts)]))
+            lw["EXPERT_OUT"] = dev(torch.stack([t(f"{q}e{e}.down") for e in range(ls.experts)]))
+            if ls.shared_ff:
+                lw["SHARED_IN"] = dev(torch.cat([t(q + "shared.gate"), t(q + "shared.up"), t(q + "shared.sg").reshape(1, -1)]))
+                lw["SHARED_OUT"] = dev(t(q + "shared.down"))
+        w["layers"].append(lw)
+    return w
+
+
+def load_hybrid_weights(path: str, spec: HybridSpec, dtype: torch.dtype, device) -> dict:
+    return pack_hybrid_weights(spec, read_safetensors(os.path.join(path, "model.safetensors")), dtype, device)
+
+
+def _i32(a):
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+class HybridRunner:
+    """Device state of one hybrid model + the one forward call every path uses (generation, trace replay, tests).
+
+    max_tokens      rows one library call carries (longer batches are cut into several calls by `forward`)
+    num_blocks      pages of the latent cache (block_size tokens each), shared by all latent-attention layers' pools
+    n_slots         recurrent-state slots (one per live sequence)"""
+
+    def __init__(self, spec: HybridSpec, weights: dict, *, dtype: str = "bfloat16", max_tokens: int = 2048, max_seqs: int = 8,
+                 block_size: int = 64, num_blocks: int = 64, n_slots: int = 8, max_model_len: int = 4096,
+                 max_logit_rows: int | None = None, device: str | torch.device = "cuda:0"):
+        if not torch.cuda.is_available():
+            raise RuntimeError("HybridRunner needs a CUDA device: libssdk has no CPU path")
+        self.lib = L.load()
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        self.spec, self.block_size, self.num_blocks, self.n_slots = spec, block_size, num_blocks, n_slots
+        self.max_tokens, self.max_seqs = max_tokens, max_seqs
+        self.max_blocks = -(-max_model_len // block_size)
+        self.max_model_len = max_model_len
+        self.dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype]
+        self.max_logit_rows = max_logit_rows or max(1, min(max_tokens, (1 << 27) // spec.vocab))
+        cfg = L.HybCfg(spec.width, spec.vocab, len(spec.layers), L.DT_BF16 if self.dtype == torch.bfloat16 else L.DT_F32,
+                       spec.eps, max_tokens, max_seqs, self.max_logit_rows, block_size, self.max_blocks, 0)
+        layer_cfgs = (L.HybLayerCfg * len(spec.layers))(*[l.cfg() for l in spec.layers])
+        h = C.c_void_p()
+        L.check(self.lib.ssdk_hyb_create(C.byref(cfg), layer_cfgs, C.byref(h)), "ssdk_hyb_create")
+        self.h = h
+        self.weights = weights
+        self._bind_weights(weights)
+        nb_c = max(0, self.lib.ssdk_hyb_cache_bytes(self.h, num_blocks))
+        nb_s = max(0, self.lib.ssdk_hyb_state_bytes(self.h, n_slots))
+        nb_w = self.lib.ssdk_hyb_workspace_bytes(self.h)
+        self.cache = torch.zeros(max(nb_c, 16), dtype=torch.uint8, device=self.device)
+        self.state = torch.zeros(max(nb_s, 16), dtype=torch.uint8, device=self.device)
+        self.workspace = torch.zeros(nb_w + 512, dtype=torch.uint8, device=self.device)
+        off = (-self.workspace.data_ptr()) % 256
+        L.check(self.lib.ssdk_hyb_bind_pools(self.h, self.cache.data_ptr(), num_blocks, self.state.data_ptr(), n_slots,
+                                             self.workspace.data_ptr() + off, nb_w), "ssdk_hyb_bind_pools")
+        self.step_id = 0
+
+    def _bind_weights(self, w: dict) -> None:
+        def bind(layer, name, t):
+            if t.dtype != self.dtype or not t.is_cuda or not t.is_contiguous():
+                raise ValueError(f"{name}: weights must be contiguous {self.dtype} CUDA tensors")
+            rows, cols = (t.shape[0], t.numel() // t.shape[0]) if t.dim() >= 2 else (t.shape[0], 1)
+            L.check(self.lib.ssdk_hyb_bind(self.h, layer, L.HT[name], t.data_ptr(), rows, cols), f"bind {name} layer {layer}")
+
+        for name in ("EMBED", "HEAD", "FINAL_NORM"):
+            bind(-1, name, w[name])
+        for i, lw in enumerate(w["layers"]):
+            for name, t in lw.items():
+                bind(i, name, t)
+
+    # ------------------------------------------------------------------ the step function
+    def forward(self, entries, *, want_logits: bool = True, temps=None, seed: int = 0, residual: bool = False):
+        """entries: list of (tokens, pos0, slot, block_table, want) — `tokens` continue a sequence at position pos0 whose
+        state lives in `slot` and whose latent rows live in the pages `block_table`; `want` lists the places among
+        `tokens` whose logits (and, with `temps`, sampled tokens) are asked for.  Returns (logits [n_want, vocab] float32
+        or None, tokens list or None[, residual [layers, rows, width]]), rows in the order of the entries."""
+        total = sum(len(e[0]) for e in entries)
+        if total > self.max_tokens or len(entries) > self.max_seqs:
+            return self._forward_split(entries, want_logits, temps, seed, residual)
+        ids, cu, pos0, slots, want_rows = [], [0], [], [], []
+        tables = np.full((len(entries), self.max_blocks), -1, dtype=np.int32)
+        for s, (toks, p0, slot, table, want) in enumerate(entries):
+            if p0 + len(toks) > self.max_model_len:
+                raise ValueError("sequence longer than max_model_len")
+            want_rows += [cu[-1] + int(k) for k in want]
+            ids += list(toks)
+            cu.append(cu[-1] + len(toks))
+            pos0.append(p0)
+            slots.append(slot)
+            tables[s, :len(table)] = table
+        n_want = len(want_rows)
+        logits = np.empty((n_want, self.spec.vocab), dtype=np.float32) if (want_logits and n_want) else None
+        toks_out = np.zeros(max(n_want, 1), dtype=np.int64)
+        temps_a = np.ascontiguousarray(temps, dtype=np.float32) if temps is not None else None
+        if temps_a is not None and len(temps_a) != n_want:
+            raise ValueError("one temperature per wanted row")
+        res = np.empty((len(self.spec.layers), total, self.spec.width), dtype=np.float32) if residual else None
+        ids_a, cu_a, pos_a, slot_a, want_a = _i32(ids), _i32(cu), _i32(pos0), _i32(slots), _i32(want_rows or [0])
+        L.check(self.lib.ssdk_hyb_forward(
+            self.h, len(entries), total, ids_a.ctypes.data_as(L.c_i32p), cu_a.ctypes.data_as(L.c_i32p),
+            pos_a.ctypes.data_as(L.c_i32p), slot_a.ctypes.data_as(L.c_i32p), tables.ctypes.data_as(L.c_i32p), n_want,
+            want_a.ctypes.data_as(L.c_i32p), logits.ctypes.data_as(L.c_f32p) if logits is not None else None,
+            temps_a.ctypes.data_as(L.c_f32p) if temps_a is not None else None, seed, self.step_id,
+            toks_out.ctypes.data_as(L.c_i64p), res.ctypes.data_as(L.c_f32p) if res is not None else None,
+            torch.cuda.current_stream().cuda_stream), "ssdk_hyb_forward")
+        self.step_id += 1
+        out = (logits, toks_out[:n_want].tolist() if temps_a is not None else None)
+        return out + (res,) if residual else out
+
+    def _forward_split(self, entries, want_logits, temps, seed, residual):
+        """A batch over the per-call limits runs as several calls: sequences are taken in order and a long portion is
+        cut, which the carried state and cache make equivalent to one call."""
+        if residual:
+            raise ValueError("the residual tap covers single calls only")
+        calls, cur, room = [], [], self.max_tokens
+        first = np.cumsum([0] + [len(e[4]) for e in entries])  # first output row of every entry
+        for i, (toks, p0, slot, table, want) in enumerate(entries):
+            lo = 0
+            while lo < len(toks):
+                if room == 0 or len(cur) == self.max_seqs:
+                    calls.append(cur)
+                    cur, room = [], self.max_tokens
+                n = min(room, len(toks) - lo)
+                js = [j for j, k in enumerate(want) if lo <= k < lo + n]
+                cur.append(([first[i] + j for j in js], (toks[lo:lo + n], p0 + lo, slot, table, [want[j] - lo for j in js])))
+                lo += n
+                room -= n
+        calls.append(cur)
+        n_out = int(first[-1])
+        logits = np.empty((n_out, self.spec.vocab), dtype=np.float32) if (want_logits and n_out) else None
+        tokens = [0] * n_out
+        for call in calls:
+            rows = [r for rs, _ in call for r in rs]
+            lg, tk = self.forward([e for _, e in call], want_logits=want_logits,
+                                  temps=[temps[r] for r in rows] if temps is not None else None, seed=seed)
+            for k, r in enumerate(rows):
+                if lg is not None:
+                    logits[r] = lg[k]
+                if tk is not None:
+                    tokens[r] = tk[k]
+        return logits, (tokens if temps is not None else None)
+
+    @property
+    def launch_count(self) -> int:
+        return int(self.lib.ssdk_hyb_launch_count(self.h))
+
+    def close(self) -> None:
+        if getattr(self, "h", None):
+            self.lib.ssdk_hyb_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

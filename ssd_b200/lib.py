@@ -38,6 +38,38 @@ class RuntimeCfg(C.Structure):
     ]
 
 
+class HybLayerCfg(C.Structure):
+    """struct ssdk_hyb_layer_cfg (include/ssdk.h)."""
+
+    _fields_ = [
+        ("mixer", C.c_int32), ("heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32),
+        ("rot_dim", C.c_int32), ("rot_dims", C.c_int32), ("kv_rank", C.c_int32), ("q_rank", C.c_int32),
+        ("decay_rank", C.c_int32), ("rot_base", C.c_float), ("attn_scale", C.c_float), ("gate_cap", C.c_float),
+        ("mlp", C.c_int32), ("experts", C.c_int32), ("top", C.c_int32), ("groups", C.c_int32), ("keep", C.c_int32),
+        ("ff", C.c_int32), ("shared_ff", C.c_int32), ("route_scale", C.c_float), ("limit", C.c_float),
+        ("shared_limit", C.c_float),
+    ]
+
+
+class HybCfg(C.Structure):
+    """struct ssdk_hyb_cfg (include/ssdk.h)."""
+
+    _fields_ = [
+        ("width", C.c_int32), ("vocab", C.c_int32), ("n_layers", C.c_int32), ("dtype", C.c_int32), ("eps", C.c_float),
+        ("max_tokens", C.c_int32), ("max_seqs", C.c_int32), ("max_logit_rows", C.c_int32), ("block_size", C.c_int32),
+        ("max_blocks_per_seq", C.c_int32), ("reserved", C.c_int32),
+    ]
+
+
+# hybrid-model enums (include/ssdk.h)
+DT_F32, DT_BF16 = 0, 1
+MIX_WKV, MIX_MLSTM, MIX_LATENT_ATTN = 0, 1, 2
+MLP_NONE, MLP_MOE = 0, 1
+HT_NAMES = ("EMBED HEAD FINAL_NORM NORM LS_MIX LS_MLP WKV_MU WKV_R WKV_K WKV_V WKV_G WKV_W1 WKV_W2 WKV_W0 WKV_U MLSTM_IN "
+            "MLSTM_IB MLSTM_FB LAT_DOWN LAT_QNORM LAT_KVNORM LAT_UQ LAT_UKT LAT_UV LAT_SINK MIX_NORM MIX_OUT ROUTER "
+            "EXPERT_IN EXPERT_OUT SHARED_IN SHARED_OUT").split()
+HT = {n: i for i, n in enumerate(HT_NAMES)}
+
 # weight kinds (enum in include/ssdk.h)
 W_EMBED, W_LM_HEAD, W_FINAL_NORM, W_INPUT_NORM, W_QKV, W_Q_NORM, W_K_NORM, W_O, W_POST_NORM, W_GATE_UP, W_DOWN, W_ROPE_TABLE = range(12)
 TARGET, DRAFT = 0, 1
@@ -83,6 +115,16 @@ SIGNATURES: dict[str, tuple] = {
     "ssdk_verify_scratch_bytes": (C.c_int64, [C.c_int, C.c_int]),
     "ssdk_verify": (C.c_int, [VP, VP, VP, VP, VP, VP, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64, C.c_uint64,
                               VP, VP, VP, VP]),
+    "ssdk_hyb_create": (C.c_int, [C.POINTER(HybCfg), C.POINTER(HybLayerCfg), C.POINTER(VP)]),
+    "ssdk_hyb_destroy": (C.c_int, [VP]),
+    "ssdk_hyb_bind": (C.c_int, [VP, C.c_int, C.c_int, VP, C.c_int64, C.c_int64]),
+    "ssdk_hyb_cache_bytes": (C.c_int64, [VP, C.c_int64]),
+    "ssdk_hyb_state_bytes": (C.c_int64, [VP, C.c_int64]),
+    "ssdk_hyb_workspace_bytes": (C.c_int64, [VP]),
+    "ssdk_hyb_bind_pools": (C.c_int, [VP, VP, C.c_int64, VP, C.c_int64, VP, C.c_int64]),
+    "ssdk_hyb_forward": (C.c_int, [VP, C.c_int, C.c_int, c_i32p, c_i32p, c_i32p, c_i32p, c_i32p, C.c_int, c_i32p, c_f32p,
+                                   c_f32p, C.c_uint64, C.c_uint64, c_i64p, c_f32p, VP]),
+    "ssdk_hyb_launch_count": (C.c_int64, [VP]),
 }
 
 _lib = None
