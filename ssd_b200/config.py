@@ -46,6 +46,9 @@ class Config:
     use_cuda_graph: bool = True
     use_pdl: bool = True
     seed: int = 0
+    # hybrid (layered) models: storage type of weights / activations and the size of the recurrent-state pool
+    dtype: str = "bfloat16"
+    num_state_slots: int = -1
 
     @property
     def max_blocks(self) -> int:
@@ -63,6 +66,19 @@ class Config:
         if self.enforce_eager:
             self.use_cuda_graph = False
         self.hf_config = load_hf_config(self.model)
+        self.family = self.hf_config.family
+        if self.family.kind == "hybrid":
+            if self.speculate:
+                raise NotImplementedError("speculative decoding is built for the dense families only")
+            if self.num_gpus != 1:
+                raise NotImplementedError("hybrid models run on one GPU")
+            if self.dtype not in ("bfloat16", "float32"):
+                raise ValueError(f"dtype={self.dtype!r}: bfloat16 or float32")
+            if self.max_num_batched_tokens < self.max_model_len:
+                raise AssertionError("max_num_batched_tokens < max_model_len (config.py:94)")
+            return
+        if self.dtype != "bfloat16":
+            raise ValueError("the dense families run in bfloat16 only")
         self.max_model_len = min(self.max_model_len, self.hf_config.max_position_embeddings)
         if self.speculate:
             if not os.path.isdir(self.draft):
@@ -94,6 +110,25 @@ class _HFConfig:
             self.rope_theta = rp.get("rope_theta", 1000000.0 if "qwen" in self.model_type else 500000.0)
 
 
-def load_hf_config(path: str) -> _HFConfig:
+class _LayeredConfig:
+    """config.json of a hybrid model: kept as the parsed dict (`raw`); ssd_b200.hybrid.HybridSpec reads it together
+    with the checkpoint's tensor shapes.  Positions are computed on the fly, so there is no positional limit."""
+
+    def __init__(self, d: dict, family):
+        self.raw, self.family = d, family
+        self.model_type = family.name
+        self.architecture = d.get("architecture")
+        self.vocab_size = int(d["vocab"])
+        self.max_position_embeddings = 1 << 30
+
+
+def load_hf_config(path: str):
+    from .registry import family_of
     with open(os.path.join(path, "config.json")) as f:
-        return _HFConfig(json.load(f))
+        d = json.load(f)
+    family = family_of(d)
+    if family.kind == "hybrid":
+        return _LayeredConfig(d, family)
+    cfg = _HFConfig(d)
+    cfg.family = family
+    return cfg

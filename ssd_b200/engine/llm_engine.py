@@ -11,7 +11,8 @@ from ..config import Config
 from ..sampling_params import SamplingParams
 from .scheduler import Scheduler
 from .sequence import Sequence
-from .step import AutoRegressiveStep, InferenceStep, SpecDecodeStep
+from .state_manager import StateSlotManager
+from .step import AutoRegressiveStep, HybridStep, InferenceStep, SpecDecodeStep
 
 METRICS = {
     "cache_hits": [],
@@ -45,7 +46,14 @@ class LLMEngine:
             if tf != df:
                 raise AssertionError("target and draft must be of the same model family (llm_engine.py:55-57)")
         self._workers = None
-        if config.num_gpus > 1:
+        self.draft_cfg = None
+        state_manager = None
+        if config.family.kind == "hybrid":
+            from ..loader import build_hybrid_runner
+            self.runner = build_hybrid_runner(config)
+            if self.runner.spec.has_state:
+                state_manager = StateSlotManager(self.runner.n_slots)
+        elif config.num_gpus > 1:
             from ..parallel import launch_tp_engine
             self.runner, self.draft_cfg, self._workers = launch_tp_engine(config, model, kwargs)
         else:
@@ -56,7 +64,9 @@ class LLMEngine:
         config.eos = getattr(self.tokenizer, "eos_token_id", -1)
         if config.eos is None:
             config.eos = -1
-        self.scheduler = Scheduler(config, draft_cfg=self.draft_cfg if config.speculate else None)
+        # recurrent layers make cached pages useless without the state that went with them: no prefix reuse there
+        self.scheduler = Scheduler(config, draft_cfg=self.draft_cfg if config.speculate else None, state_manager=state_manager,
+                                   prefix_reuse=config.family.kind != "hybrid")
         self._exiting = False
         atexit.register(self.exit)
 
@@ -85,6 +95,8 @@ class LLMEngine:
         self.scheduler.add(Sequence(prompt, sampling_params))
 
     def create_inference_step(self, config: Config) -> InferenceStep:
+        if config.family.kind == "hybrid":
+            return HybridStep(self.scheduler, self.runner, self.tokenizer, config.seed)
         if config.speculate:
             return SpecDecodeStep(self.scheduler, self.runner, config.speculate_k, METRICS, self.tokenizer, config.seed)
         return AutoRegressiveStep(self.scheduler, self.runner, self.tokenizer, config.seed)
@@ -167,11 +179,27 @@ class LLMEngine:
         return outs, METRICS
 
 
+class IdTokenizer:
+    """Stand-in for checkpoints that ship no tokenizer: text is a list of token ids written in decimal."""
+    eos_token_id = None
+
+    def __init__(self, vocab: int):
+        self.vocab = vocab
+
+    def encode(self, text: str) -> list[int]:
+        return [int(t) % self.vocab for t in text.split()]
+
+    def decode(self, ids) -> str:
+        return " ".join(str(int(i)) for i in ids)
+
+
 def _load_tokenizer(config):
     """AutoTokenizer.from_pretrained(config.model) (llm_engine.py:116); synthetic model directories ship a
     WordLevel tokenizer.json, read directly with `tokenizers` to avoid transformers' network probes."""
     import os
     path = config.tokenizer_path or config.model
+    if config.family.kind == "hybrid" and not os.path.exists(os.path.join(path, "tokenizer.json")):
+        return IdTokenizer(config.hf_config.vocab_size)
     marker = os.path.join(path, "ssd_b200_synthetic.json")
     if os.path.exists(marker):
         from ..synth import SyntheticTokenizer

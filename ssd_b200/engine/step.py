@@ -46,6 +46,35 @@ class AutoRegressiveStep(InferenceStep):
         return len(seqs)
 
 
+class HybridStep(InferenceStep):
+    """Autoregressive generation with a hybrid model: every call is ONE ragged batch through HybridRunner.forward —
+    `run` is the step function that generation, chunked prefill and trace replay share."""
+
+    def __init__(self, scheduler, runner, tokenizer=None, seed: int = 0):
+        super().__init__(scheduler)
+        self.runner, self.tokenizer, self.seed = runner, tokenizer, seed
+
+    def run(self, portions, *, want_logits: bool = False, sample: bool = True):
+        """portions: list of (seq, first position, number of tokens, wanted places among them).  The tokens are taken
+        from seq.token_ids; pages and the state slot from the sequence.  Returns (logits or None, tokens or None)."""
+        entries, temps = [], []
+        for seq, pos0, n, want in portions:
+            entries.append((seq.token_ids[pos0:pos0 + n], pos0, max(seq.state_slot, 0), seq.block_table, want))
+            temps += [seq.temperature] * len(want)
+        return self.runner.forward(entries, want_logits=want_logits, temps=temps if sample else None, seed=self.seed)
+
+    def prefill(self, seqs) -> int:
+        _, toks = self.run([(s, s.num_cached_tokens, len(s) - s.num_cached_tokens, [len(s) - s.num_cached_tokens - 1])
+                            for s in seqs])
+        self.scheduler.postprocess(seqs, toks, True)
+        return sum(len(s) for s in seqs)
+
+    def decode(self, seqs) -> int:
+        _, toks = self.run([(s, len(s) - 1, 1, [0]) for s in seqs])
+        self.scheduler.postprocess(seqs, toks, False)
+        return len(seqs)
+
+
 class SpecDecodeStep(InferenceStep):
     """engine/step.py:56-163 for synchronous speculation."""
 

@@ -137,6 +137,25 @@ def kv_blocks_for(config, spec: ModelSpec, tp_size: int, share: float, reserved:
     return max(1, min(fit, want))
 
 
+def build_hybrid_runner(config, device=None):
+    """HybridRunner for a hybrid checkpoint directory: the pools are sized from the Config like the dense path's KV
+    cache (pages for max_num_seqs sequences of max_model_len unless num_kvcache_blocks says otherwise; one state slot
+    per running sequence unless num_state_slots says otherwise)."""
+    from .hybrid import HybridRunner, HybridSpec, load_hybrid_weights
+    device = torch.device(device or "cuda:0")
+    torch.cuda.set_device(device)
+    spec = HybridSpec.from_dir(config.model)
+    dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[config.dtype]
+    weights = load_hybrid_weights(config.model, spec, dtype, device)
+    seqs = max(1, config.max_num_seqs)
+    if config.num_kvcache_blocks <= 0:
+        config.num_kvcache_blocks = seqs * config.max_blocks
+    slots = config.num_state_slots if config.num_state_slots > 0 else seqs
+    return HybridRunner(spec, weights, dtype=config.dtype, max_tokens=min(config.max_num_batched_tokens, 4096), max_seqs=seqs,
+                        block_size=config.kvcache_block_size, num_blocks=config.num_kvcache_blocks, n_slots=slots,
+                        max_model_len=config.max_model_len, device=device)
+
+
 def build_runner(config, tp_size: int = 1, tp_rank: int = 0, device=None, finalize: bool = True):
     device = torch.device(device or "cuda:0")
     torch.cuda.set_device(device)
