@@ -45,6 +45,21 @@ struct ssdk_hyb_engine {
   int w_p0 = 0, w_p1 = 0, w_p2 = 0, w_p3 = 0, w_t0 = 0, w_t1 = 0, w_e = 0, w_top = 0, w_ff2 = 0, w_ff = 0, w_sff2 = 0, w_sff = 0;
   bool any_wkv = false;
   int* h_meta = nullptr;     // pinned staging of the step's integers
+  // tcgen05 path of the dense bf16 products: TMA descriptors by (pointer, rows, K, box rows), split-K partials
+  bool use_tc = true;
+  std::map<std::tuple<const void*, int64_t, int, int>, CUtensorMap> tmaps;
+  float* partials = nullptr; size_t partial_floats = 0;
+  int tmap(const void* ptr, int64_t rows, int K, int box_rows, const CUtensorMap** out) {
+    auto key = std::make_tuple(ptr, rows, K, box_rows);
+    auto it = tmaps.find(key);
+    if (it == tmaps.end()) {
+      CUtensorMap tm;
+      CKI(make_tmap(&tm, ptr, rows, K, box_rows));
+      it = tmaps.emplace(key, tm).first;
+    }
+    *out = &it->second;
+    return 0;
+  }
   int64_t launches = 0;
   bool smem_attr_done = false;
 };
@@ -132,6 +147,11 @@ static int64_t hyb_carve(ssdk_hyb_engine* e, uint8_t* base) {
   e->temps = (float*)take(lr * 4);
   e->meta_ints = 2 * cap + 3 * (size_t)g.max_seqs + 1 + (size_t)g.max_seqs * g.max_blocks_per_seq + lr;
   e->meta = (int*)take(e->meta_ints * 4);
+  // split-K partials of the tcgen05 GEMM at <= 64 rows: up to 8 splits of the widest output, bounded at 32 MB
+  size_t widest = std::max<size_t>(g.vocab, g.width);
+  for (int w : {e->w_p0, e->w_p1, e->w_sff2}) widest = std::max<size_t>(widest, (size_t)w);
+  e->partial_floats = es == 2 ? std::min<size_t>(8 * 64 * widest, 8u << 20) : 0;
+  e->partials = (float*)take(e->partial_floats * 4);
   return (int64_t)off;
 }
 
@@ -145,11 +165,47 @@ struct HybRun {
   template <typename OutT>
   int lin_args(const ssdk::LinearArgs& a, int rows_hint, int batch) {
     dim3 grid((a.N + ssdk::kLinBN - 1) / ssdk::kLinBN, a.tile_expert ? e->max_tiles : (rows_hint + ssdk::kLinBM - 1) / ssdk::kLinBM, batch);
+    if constexpr (std::is_same<T, bf16>::value) {
+      const bool vec = a.K % 8 == 0 && a.lda % 8 == 0 && a.ldw % 8 == 0 && a.sA % 8 == 0 && a.sW % 8 == 0 && a.sW_expert % 8 == 0 &&
+                       ((uintptr_t)a.A & 15) == 0 && ((uintptr_t)a.W & 15) == 0;
+      if (vec) return L.go(ssdk::linear_mma_kernel<OutT>, grid, dim3(ssdk::kMmaThreads), 0, a);
+    }
     return L.go(ssdk::linear_kernel<T, OutT>, grid, dim3(ssdk::kLinThreads), 0, a);
+  }
+  // dense bf16 product on the tcgen05 GEMM of gemm.cuh (swap-AB, TMA-fed, fp32 out): K a multiple of 64, dense rows
+  bool tc_ok(const void* A, int lda, const void* W, int ldw, int ldc, int N, int K) const {
+    return std::is_same<T, bf16>::value && e->use_tc && K % kBlockK == 0 && lda == K && ldw == K && ldc == N &&
+           ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0;
+  }
+  int lin_tc(const void* A, const void* W, float* C, int m_total, int N, int K) {
+    const CUtensorMap* tmW;
+    CKI(e->tmap(W, N, K, 64, &tmW));
+    const int tiles = (N + kTileRows - 1) / kTileRows, num_kb = K / kBlockK;
+    for (int r0 = 0; r0 < m_total; r0 += kMaxTokens) {
+      const int m = std::min(kMaxTokens, m_total - r0), un = umma_n_for(m);
+      const CUtensorMap* tmX;
+      CKI(e->tmap((const bf16*)A + (size_t)r0 * K, m, K, un, &tmX));
+      int S = m <= 64 ? auto_splits(tiles, num_kb, 2) : 1;
+      while (S > 1 && (size_t)S * m * N > e->partial_floats) --S;
+      GemmParams p;
+      p.M = m; p.N = N; p.ldo = N; p.num_kb = num_kb; p.tile_rows = kTileRows; p.hi_row_offset = 64;
+      p.sk_partials = nullptr; p.sk_counters = nullptr; p.sk_width = 0;
+      p.kb_per_split = (num_kb + S - 1) / S;
+      S = (num_kb + p.kb_per_split - 1) / p.kb_per_split;
+      float* dst = C + (size_t)r0 * N;
+      p.out = S == 1 ? dst : e->partials;
+      CKI(launch_gemm(L, un, EPI_PARTIAL, *tmW, *tmX, p, tiles, S));
+      if (S > 1) {
+        const size_t n = (size_t)m * N;
+        CKI(L.go(ssdk::splitk_sum_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (const float*)e->partials, dst, S, n));
+      }
+    }
+    return 0;
   }
   // C[M, N] (fp32 unless out_t) = A[M, K] W[N, K]^T
   int lin(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int m, int N, int K, bool out_t = false,
           int batch = 1, long long sA = 0, long long sW = 0, long long sC = 0) {
+    if (!out_t && batch == 1 && tc_ok(A, lda, W, ldw, ldc, N, K)) return lin_tc(A, W, (float*)C, m, N, K);
     ssdk::LinearArgs a = {};
     a.A = A; a.W = W; a.C = C; a.M = m; a.N = N; a.K = K; a.lda = lda; a.ldw = ldw; a.ldc = ldc;
     a.sA = sA; a.sW = sW; a.sC = sC;
@@ -400,6 +456,7 @@ int ssdk_hyb_create(const ssdk_hyb_cfg* cfg, const ssdk_hyb_layer_cfg* layers, s
   auto* e = new ssdk_hyb_engine();
   e->cfg = *cfg;
   e->esz = cfg->dtype == SSDK_DT_BF16 ? 2 : 4;
+  e->use_tc = env_int("SSDK_HYB_TCGEN05", 1) != 0;
   e->layers.resize(cfg->n_layers);
   for (int i = 0; i < cfg->n_layers; ++i) e->layers[i].c = layers[i];
   if (hyb_derive(e) != 0) { delete e; return -1; }

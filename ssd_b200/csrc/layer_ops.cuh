@@ -109,6 +109,15 @@ __global__ void f32_to_bf16_kernel(const float* __restrict__ z, __nv_bfloat16* _
     y[i] = __float2bfloat16_rn(z[i]);
 }
 
+// out[i] = sum over s of partials[s][i] in the fixed order s = 0 .. S-1 (split-K of the tcgen05 GEMM, fp32)
+__global__ void splitk_sum_kernel(const float* __restrict__ partials, float* __restrict__ out, int S, size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float a = partials[i];
+  for (int s = 1; s < S; ++s) a += partials[(size_t)s * n + i];
+  out[i] = a;
+}
+
 struct CombineArgs {
   float* x;              // [M, width] residual, updated in place
   const float* mix;      // [M, width] mixer output (after its output projection)

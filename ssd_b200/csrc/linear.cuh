@@ -1,18 +1,21 @@
 // linear.cuh — shape-generic linear layers for the layered (hybrid) models: C[M,N] = A[M,K] · W[N,K]^T with fp32
 // accumulation for ANY M, N, K (head sizes such as 40 or 48 have no 64-column TMA box), in two storage types:
 //   T = bf16 : operands bf16, products exact in fp32, fp32 accumulate (the rounding contract of a tensor-core GEMM);
-//              tile products on mma.sync.m16n8k16 when K is a multiple of 16, CUDA-core FMA otherwise
+//              tile products on mma.sync.m16n8k16 when rows are 16-byte aligned (K, strides multiples of 8),
+//              CUDA-core FMA otherwise
 //   T = float: true fp32 FMA (no TF32), used by the exact mode
 // Three addressing modes share one kernel: dense, batched (blockIdx.z walks per-head slices by strides) and grouped
 // (a tile list made on the device by the router maps tile -> expert / first row / row count; the rows of A may be
 // gathered through an index).  The accumulation order of an output element depends on K alone, never on M or on which
 // other rows share the tile, so a token's result is independent of the batch it ran in.
-// Large aligned bf16 products take the tcgen05 path of gemm.cuh instead (see enqueue_linear in hybrid_engine.cuh).
+// Dense bf16 products with K a multiple of 64 take the tcgen05 path of gemm.cuh instead (HybRun::lin in
+// hybrid_engine.cuh); this file serves the shapes a 64-column TMA box cannot: odd sizes, per-head slices, gathered rows.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "attention.cuh"
 #include "common.cuh"
 
 namespace ssdk {
@@ -114,6 +117,104 @@ __global__ void __launch_bounds__(kLinThreads) linear_kernel(const LinearArgs p)
       if (c < p.N) st_f<OutT>(C + (long long)(row0 + r) * p.ldc + c, acc[i][j]);
     }
   }
+}
+
+// Tensor-core tile for bf16 (legacy mma.sync path; operands need 16-byte aligned rows: K, lda, ldw and the batch strides
+// multiples of 8).  64 x 64 outputs per CTA, four warps of 32 x 32, k-steps of 32 staged through padded shared memory
+// (row stride 80 B: ldmatrix rows fall into distinct 16-byte bank groups) with the next step's global loads in
+// registers while the current one is multiplied.
+constexpr int kMmaThreads = 128, kMmaBK = 32, kMmaLd = kMmaBK + 8;
+
+template <typename OutT>
+__global__ void __launch_bounds__(kMmaThreads) linear_mma_kernel(const LinearArgs p) {
+  typedef __nv_bfloat16 T;
+  __shared__ __align__(16) T As[kLinBM][kMmaLd];
+  __shared__ __align__(16) T Ws[kLinBN][kMmaLd];
+  int row0, nrows;
+  const T* W = (const T*)p.W + (long long)blockIdx.z * p.sW;
+  const T* A = (const T*)p.A + (long long)blockIdx.z * p.sA;
+  OutT* C = (OutT*)p.C + (long long)blockIdx.z * p.sC;
+  if (p.tile_expert) {
+    if ((int)blockIdx.y >= *p.n_tiles) return;
+    W += (long long)p.tile_expert[blockIdx.y] * p.sW_expert;
+    row0 = p.tile_row0[blockIdx.y];
+    nrows = p.tile_rows[blockIdx.y];
+  } else {
+    row0 = blockIdx.y * kLinBM;
+    nrows = min(kLinBM, p.M - row0);
+    if (nrows <= 0) return;
+  }
+  const int col0 = blockIdx.x * kLinBN;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, wm = warp >> 1, wn = warp & 1;
+  // staging: vector v = tid + i * 128 -> row v / 4, k offset (v % 4) * 8
+  const T* a_src[2];
+  const T* w_src[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int v = tid + i * kMmaThreads, r = v >> 2, kv = (v & 3) * 8;
+    int ar = row0 + r;
+    const bool aok = r < nrows;
+    if (aok && p.a_rows) ar = p.a_rows[ar];
+    a_src[i] = aok ? A + (long long)ar * p.lda + kv : nullptr;
+    w_src[i] = (col0 + r < p.N) ? W + (long long)(col0 + r) * p.ldw + kv : nullptr;
+  }
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc[i][j][k] = 0.f;
+  uint4 ra[2], rw[2];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int kv = ((tid + i * kMmaThreads) & 3) * 8;
+      const bool kin = k0 + kv < p.K;
+      ra[i] = (a_src[i] && kin) ? *reinterpret_cast<const uint4*>(a_src[i] + k0) : make_uint4(0, 0, 0, 0);
+      rw[i] = (w_src[i] && kin) ? ld_nc_v4(w_src[i] + k0) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  fetch(0);
+  for (int k0 = 0; k0 < p.K; k0 += kMmaBK) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int v = tid + i * kMmaThreads, r = v >> 2, kv = (v & 3) * 8;
+      *reinterpret_cast<uint4*>(&As[r][kv]) = ra[i];
+      *reinterpret_cast<uint4*>(&Ws[r][kv]) = rw[i];
+    }
+    __syncthreads();
+    if (k0 + kMmaBK < p.K) fetch(k0 + kMmaBK);
+#pragma unroll
+    for (int kk = 0; kk < kMmaBK; kk += 16) {
+      uint32_t a[2][4], b[2][4];
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi) ldmatrix_x4(a[mi], &As[wm * 32 + mi * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+#pragma unroll
+      for (int nj = 0; nj < 2; ++nj)
+        ldmatrix_x4(b[nj], &Ws[wn * 32 + nj * 16 + (lane >> 4) * 8 + (lane & 7)][kk + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int ni = 0; ni < 4; ++ni) mma_bf16_16816(acc[mi][ni], a[mi], b[ni >> 1][(ni & 1) * 2], b[ni >> 1][(ni & 1) * 2 + 1]);
+    }
+    __syncthreads();
+  }
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = wm * 32 + mi * 16 + g + half * 8;
+      if (r >= nrows) continue;
+#pragma unroll
+      for (int ni = 0; ni < 4; ++ni) {
+        const int c = col0 + wn * 32 + ni * 8 + 2 * t;
+        OutT* dst = C + (long long)(row0 + r) * p.ldc + c;
+        if (c < p.N) st_f<OutT>(dst, acc[mi][ni][half * 2]);
+        if (c + 1 < p.N) st_f<OutT>(dst + 1, acc[mi][ni][half * 2 + 1]);
+      }
+    }
 }
 
 }  // namespace ssdk

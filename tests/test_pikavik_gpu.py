@@ -212,11 +212,15 @@ def test_long_batches_are_split_into_calls(tmp_path):
         assert U.rel_err(lg[2 * i:2 * i + 2], ref[[0, len(s) - 1]]) < F32_TOL
 
 
-def test_bfloat16_storage(tmp_path):
+@pytest.mark.parametrize("width", [40, 128, 36], ids=["rows-16B-aligned", "tcgen05-shapes", "unaligned"])
+def test_bfloat16_storage(tmp_path, width):
     """bf16 weights / activations / cache with fp32 accumulation, residual, state and scores.  Every expert is chosen
-    (top == experts), so no routing decision can flip between the oracle and the rounded run."""
+    (top == experts), so no routing decision can flip between the oracle and the rounded run.  The width picks the
+    product kernel: 128 puts the dense projections on the tcgen05 GEMM, 40 on the mma.sync tile, 36 on the FMA tile."""
     every = dict(experts=4, top=4, groups=2, keep=2)
-    cfg = U.config([U.mlstm(mlp=U.moe(**every)), U.wkv(mlp=U.moe(**every)), U.latent(mlp=U.moe(**every)), U.wkv(), U.mlstm(heads=3, dim=6, vdim=11)])
+    cfg = U.config([U.mlstm(mlp=U.moe(**every)), U.wkv(mlp=U.moe(**every)), U.latent(mlp=U.moe(**every)), U.wkv(),
+                    U.mlstm(heads=3, dim=6, vdim=11), U.wkv(heads=2, dim=32, rank=64), U.latent(heads=2, dim=32, rot_dim=16, vdim=32, kv_rank=64, q_rank=64)],
+                   width=width)
     r, plain, _ = _runner(tmp_path, cfg, dtype="bfloat16")
     n = 120
     toks = _tokens(n, cfg["vocab"], 60)
