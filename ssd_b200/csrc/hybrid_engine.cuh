@@ -32,8 +32,11 @@ struct ssdk_hyb_engine {
   float* state = nullptr; int64_t n_slots = 0;
   // workspace carve
   int64_t ws_bytes = 0;
-  float *x = nullptr, *p0 = nullptr, *p1 = nullptr, *p2 = nullptr, *p3 = nullptr, *mix_out = nullptr;
+  float *x = nullptr, *p0 = nullptr, *p1 = nullptr, *p2 = nullptr, *mix_out = nullptr;
   void *h = nullptr, *mixes = nullptr, *t0 = nullptr, *t1 = nullptr;
+  // latent attention: concatenated queries, one sequence's gathered keys / transposed latents, score and weight blocks
+  void *qcat = nullptr, *keys = nullptr, *lat_t = nullptr, *att_p = nullptr; float* att_s = nullptr;
+  size_t att_elems = 0; int w_qcat = 0, w_key = 0, w_kr = 0, w_lh = 0;
   float *rz = nullptr, *wts = nullptr, *eg = nullptr, *eo = nullptr, *sz = nullptr, *so = nullptr;
   void *ey = nullptr, *sy = nullptr;
   int *sel = nullptr, *apos = nullptr, *arow = nullptr, *tile_expert = nullptr, *tile_row0 = nullptr, *tile_rows = nullptr,
@@ -42,7 +45,7 @@ struct ssdk_hyb_engine {
   int* meta = nullptr; size_t meta_ints = 0;
   int max_tiles = 0;
   // widths of the shared buffers (elements per row)
-  int w_p0 = 0, w_p1 = 0, w_p2 = 0, w_p3 = 0, w_t0 = 0, w_t1 = 0, w_e = 0, w_top = 0, w_ff2 = 0, w_ff = 0, w_sff2 = 0, w_sff = 0;
+  int w_p0 = 0, w_p1 = 0, w_p2 = 0, w_t0 = 0, w_t1 = 0, w_e = 0, w_top = 0, w_ff2 = 0, w_ff = 0, w_sff2 = 0, w_sff = 0;
   bool any_wkv = false;
   int* h_meta = nullptr;     // pinned staging of the step's integers
   // tcgen05 path of the dense bf16 products: TMA descriptors by (pointer, rows, K, box rows), split-K partials
@@ -89,7 +92,8 @@ static int hyb_derive(ssdk_hyb_engine* e) {
       L.cache_rows_before = crow;
       crow += L.cache_row;
       up(e->w_p0, (long long)c.q_rank + c.kv_rank + c.rot_dim); up(e->w_p1, (long long)H * (D + c.rot_dim));
-      up(e->w_p2, (long long)H * c.rot_dim); up(e->w_p3, (long long)H * c.kv_rank);
+      up(e->w_qcat, (long long)H * (c.kv_rank + c.rot_dim)); up(e->w_key, (long long)c.kv_rank + c.rot_dim);
+      up(e->w_kr, c.kv_rank); up(e->w_lh, H);
       up(e->w_t0, std::max((long long)c.q_rank, (long long)H * c.kv_rank)); up(e->w_t1, std::max((long long)H * D, (long long)H * V));
     } else {
       return fail("hybrid layer: unknown mixer %d", c.mixer);
@@ -122,10 +126,19 @@ static int64_t hyb_carve(ssdk_hyb_engine* e, uint8_t* base) {
   e->p0 = (float*)take(cap * e->w_p0 * 4);
   e->p1 = (float*)take(cap * e->w_p1 * 4);
   e->p2 = (float*)take(cap * e->w_p2 * 4);
-  e->p3 = (float*)take(cap * e->w_p3 * 4);
   e->t0 = take(cap * e->w_t0 * es);
   e->t1 = take(cap * e->w_t1 * es);
   e->mix_out = (float*)take(cap * g.width * 4);
+  {
+    const size_t ctx_pad = align_up((size_t)g.max_blocks_per_seq * g.block_size, 8);
+    e->qcat = take(cap * e->w_qcat * es);
+    e->keys = take(e->w_key ? ctx_pad * e->w_key * es : 0);
+    e->lat_t = take(e->w_kr ? ctx_pad * e->w_kr * es : 0);
+    // one query block's scores (fp32) and weights (T): as many queries as fit 24 M elements, at least one
+    e->att_elems = e->w_lh ? std::max((size_t)e->w_lh * ctx_pad, std::min(cap * e->w_lh * ctx_pad, (size_t)24 << 20)) : 0;
+    e->att_s = (float*)take(e->att_elems * 4);
+    e->att_p = take(e->att_elems * es);
+  }
   e->rz = (float*)take(cap * e->w_e * 4);
   e->wts = (float*)take(A * 4);
   e->sel = (int*)take(A * 4); e->apos = (int*)take(A * 4); e->arow = (int*)take(A * 4);
@@ -160,6 +173,7 @@ struct HybRun {
   ssdk_hyb_engine* e;
   Launcher L;
   ssdk::Ragged rg;
+  const int32_t *h_cu = nullptr, *h_pos0 = nullptr;  // host copies of the row offsets and first positions
   int M;
 
   template <typename OutT>
@@ -204,8 +218,8 @@ struct HybRun {
   }
   // C[M, N] (fp32 unless out_t) = A[M, K] W[N, K]^T
   int lin(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int m, int N, int K, bool out_t = false,
-          int batch = 1, long long sA = 0, long long sW = 0, long long sC = 0) {
-    if (!out_t && batch == 1 && tc_ok(A, lda, W, ldw, ldc, N, K)) return lin_tc(A, W, (float*)C, m, N, K);
+          int batch = 1, long long sA = 0, long long sW = 0, long long sC = 0, bool allow_tc = true) {
+    if (allow_tc && !out_t && batch == 1 && tc_ok(A, lda, W, ldw, ldc, N, K)) return lin_tc(A, W, (float*)C, m, N, K);
     ssdk::LinearArgs a = {};
     a.A = A; a.W = W; a.C = C; a.M = m; a.N = N; a.K = K; a.lda = lda; a.ldw = ldw; a.ldc = ldc;
     a.sA = sA; a.sW = sW; a.sC = sC;
@@ -298,20 +312,25 @@ struct HybRun {
     pa.eps = e->cfg.eps;
     CKI(L.go(ssdk::latent_prep_kernel<T>, dim3(M), dim3(128), 0, pa, rg));
     CKI(lin(e->t0, QR, Lr.t[SSDK_HT_LAT_UQ].p, QR, e->p1, H * (D + R), M, H * (D + R), QR));
-    CKI(L.go(ssdk::latent_q_kernel<T>, dim3(M, H), dim3(64), 0, (const float*)e->p1, (T*)e->t1, e->p2, (const float*)Lr.inv_freq, rg,
-             H, D, R, c.rot_dims));
-    // absorption: qlat[m, h, :] = W_uk,h^T qn[m, h, :]
-    CKI(lin(e->t1, H * D, Lr.t[SSDK_HT_LAT_UKT].p, D, e->p3, H * KR, M, KR, D, false, H, D, (long long)KR * D, KR));
-    ssdk::LatentAttnArgs aa;
-    aa.qlat = e->p3; aa.qr = e->p2; aa.cache = pool; aa.sink = Lr.t[SSDK_HT_LAT_SINK].p; aa.out = e->t0;
-    aa.H = H; aa.kv_rank = KR; aa.R = R; aa.scale = c.attn_scale;
-    const int Wd = KR + R, Wp = Wd | 1;
-    int hg = std::min(H, 16);
-    auto smem_of = [&](int g) { return (size_t)(g * Wd + ssdk::kLatKC * Wp + g * KR + g * ssdk::kLatKC + 3 * g) * 4; };
-    while (hg > 1 && smem_of(hg) > 200 * 1024) hg = (hg + 1) / 2;
-    if (smem_of(hg) > 200 * 1024) return fail("latent attention: row width %d too large for shared memory", Wd);
-    aa.hg = hg;
-    CKI(L.go(ssdk::latent_attn_kernel<T>, dim3(M, (H + hg - 1) / hg), dim3(ssdk::kLatThreads), smem_of(hg), aa, rg));
+    const int Wd = KR + R;
+    CKI(L.go(ssdk::latent_q_kernel<T>, dim3(M, H), dim3(64), 0, (const float*)e->p1, (T*)e->t1, (T*)e->qcat, (const float*)Lr.inv_freq, rg,
+             H, D, R, KR, c.rot_dims));
+    // absorption: qcat[m, h, :kv_rank] = W_uk,h^T qn[m, h, :]
+    CKI(lin(e->t1, H * D, Lr.t[SSDK_HT_LAT_UKT].p, D, e->qcat, H * Wd, M, KR, D, true, H, D, (long long)KR * D, Wd));
+    for (int s = 0; s < rg.n_seqs; ++s) {
+      const int r0 = h_cu[s], n = h_cu[s + 1] - r0, p0 = h_pos0[s], ctx = p0 + n, ctx_pad = (ctx + 7) / 8 * 8;
+      CKI(L.go(ssdk::latent_gather_kernel<T>, dim3(ctx_pad), dim3(128), 0, (const T*)pool, (T*)e->keys, (T*)e->lat_t, rg, s, ctx, ctx_pad,
+               KR, Wd));
+      const int qb = (int)std::max<size_t>(1, e->att_elems / ((size_t)H * ctx_pad));
+      for (int q0 = 0; q0 < n; q0 += qb) {
+        const int nq = std::min(qb, n - q0), rows = nq * H, cb = (p0 + q0 + nq + 7) / 8 * 8;  // keys this block can see, padded
+        const T* qrows = (const T*)e->qcat + (size_t)(r0 + q0) * H * Wd;
+        CKI(lin(qrows, Wd, e->keys, Wd, e->att_s, cb, rows, cb, Wd, false, 1, 0, 0, 0, false));
+        CKI(L.go(ssdk::sink_softmax_kernel<T>, dim3(rows), dim3(256), 0, (const float*)e->att_s, (T*)e->att_p,
+                 (const T*)Lr.t[SSDK_HT_LAT_SINK].p, H, cb, p0 + q0, c.attn_scale));
+        CKI(lin(e->att_p, cb, e->lat_t, ctx_pad, (T*)e->t0 + (size_t)(r0 + q0) * H * KR, KR, rows, KR, cb, true, 1, 0, 0, 0, false));
+      }
+    }
     // per-head value projection of the latent output, rounded to T for the output projection
     CKI(lin(e->t0, H * KR, Lr.t[SSDK_HT_LAT_UV].p, KR, e->t1, H * V, M, V, KR, true, H, KR, (long long)V * KR, V));
     return lin(e->t1, H * V, Lr.t[SSDK_HT_MIX_OUT].p, H * V, e->mix_out, W, M, W, H * V);
@@ -377,8 +396,6 @@ static int hyb_smem_attrs(ssdk_hyb_engine* e) {
   CK(cudaFuncSetAttribute(ssdk::wkv_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   CK(cudaFuncSetAttribute(ssdk::mlstm_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   CK(cudaFuncSetAttribute(ssdk::mlstm_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-  CK(cudaFuncSetAttribute(ssdk::latent_attn_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-  CK(cudaFuncSetAttribute(ssdk::latent_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   e->smem_attr_done = true;
   return 0;
 }
@@ -406,7 +423,7 @@ static int hyb_forward_t(ssdk_hyb_engine* e, int n_seqs, int M, const int32_t* i
   const size_t o_want = o; if (n_want) memcpy(hm + o, want_rows, (size_t)n_want * 4); o += n_want;
   CK(cudaMemcpyAsync(d, hm, o * 4, cudaMemcpyHostToDevice, st));
   HybRun<T> run;
-  run.e = e; run.L.st = st; run.L.pdl = false; run.M = M;
+  run.e = e; run.L.st = st; run.L.pdl = false; run.M = M; run.h_cu = cu; run.h_pos0 = pos0;
   run.rg.cu = d + o_cu; run.rg.pos0 = d + o_pos; run.rg.slot = d + o_slot; run.rg.tok_seq = d + o_seq; run.rg.tables = d + o_tab;
   run.rg.n_seqs = n_seqs; run.rg.M = M; run.rg.max_blocks = g.max_blocks_per_seq; run.rg.block_size = g.block_size;
   CKI(run.L.go(ssdk::embed_rows_kernel<T>, dim3(M), dim3(128), 0, (const int*)(d + o_ids), (const T*)e->embed.p, e->x, g.width, g.vocab));

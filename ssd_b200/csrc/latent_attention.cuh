@@ -9,10 +9,13 @@
 //
 //   latent_prep_kernel   splits the fused down-projection: RMS-norm -> query latent (T); RMS-norm -> c and
 //                        rotate-half RoPE (fp32 angles) -> rotated key part, both scattered into the page slot
-//   latent_q_kernel      per head: unrotated query part -> T (operand of the absorption GEMM), rotated part -> RoPE, fp32
-//   latent_attn_kernel   one CTA per (row, head group): causal over the cache up to the row's own position; scores,
-//                        online softmax and the accumulators are fp32; the running maximum starts at the sink logit and
-//                        the running sum at 1, i.e. the sink is one more term of the denominator with no key and no value
+//   latent_q_kernel      per head: unrotated query part -> T (operand of the absorption GEMM), rotated part -> RoPE;
+//                        absorbed and rotated parts share one row [kv_rank + rot_dim] per (token, head)
+//   attention proper     per sequence and query block, as two tensor-core GEMMs around a softmax (HybRun::latent):
+//                        latent_gather_kernel (pages -> contiguous keys and transposed latents), scores = Q K^T with the
+//                        (token, head) pairs as rows (every head meets the same keys: multi-query), sink_softmax_kernel
+//                        (fp32: causal edge per row, the sink as one more term of the denominator with no key and no
+//                        value), output = P C.  Accumulation runs over keys in index order, whatever the portion.
 #pragma once
 #include "layer_ops.cuh"
 
@@ -68,10 +71,11 @@ __global__ void latent_prep_kernel(const LatentPrepArgs p, const Ragged rg) {
   }
 }
 
-// q [M, H, D + R] fp32 -> qn [M, H, D] (T), qr [M, H, R] fp32 rotated
+// q [M, H, D + R] fp32 -> qn [M, H, D] (T, operand of the absorption GEMM) and the rotated part (T) into columns
+// [kv_rank, kv_rank + R) of the concatenated query rows qcat [M, H, kv_rank + R]; the absorption GEMM fills the rest
 template <typename T>
-__global__ void latent_q_kernel(const float* __restrict__ q, T* __restrict__ qn, float* __restrict__ qr,
-                                const float* __restrict__ inv_freq, const Ragged rg, int H, int D, int R, int rot_dims) {
+__global__ void latent_q_kernel(const float* __restrict__ q, T* __restrict__ qn, T* __restrict__ qcat,
+                                const float* __restrict__ inv_freq, const Ragged rg, int H, int D, int R, int KR, int rot_dims) {
   const int m = blockIdx.x, hd = blockIdx.y, s = rg.tok_seq[m];
   const int pos = rg.pos0[s] + (m - rg.cu[s]);
   const float* src = q + ((size_t)m * H + hd) * (D + R);
@@ -86,94 +90,47 @@ __global__ void latent_q_kernel(const float* __restrict__ q, T* __restrict__ qn,
       sincosf((float)pos * inv_freq[i], &sn, &cs);
       out = c < half ? zr[c] * cs - zr[c + half] * sn : zr[c] * cs + zr[c - half] * sn;
     }
-    qr[((size_t)m * H + hd) * R + c] = out;
+    st_f<T>(qcat + ((size_t)m * H + hd) * (KR + R) + KR + c, out);
   }
 }
 
-struct LatentAttnArgs {
-  const float* qlat;  // [M, H, kv_rank] fp32 absorbed queries
-  const float* qr;    // [M, H, R] fp32 rotated queries
-  const void* cache;  // [rows, kv_rank + R] T
-  const void* sink;   // [H] T
-  void* out;          // [M, H, kv_rank] T
-  int H, kv_rank, R, hg;  // hg = heads per CTA
-  float scale;
-};
-constexpr int kLatKC = 32;       // keys per chunk
-constexpr int kLatThreads = 256;
-
-// dynamic shared memory: q [hg][W] | keys [KC][Wp] | acc [hg][kv_rank] | sc [hg][KC] | m, l, f [hg] each;  W = kv_rank + R,
-// Wp = W | 1 (odd row stride: the score loop reads one key row per thread)
+// One sequence's cached rows, made contiguous for the two attention GEMMs: keys [ctx_pad, W] (W = kv_rank + R) and the
+// latents transposed, lat_t [kv_rank, ctx_pad]; rows / columns from ctx up to ctx_pad (a multiple of 8) are zero.
 template <typename T>
-__global__ void __launch_bounds__(kLatThreads) latent_attn_kernel(const LatentAttnArgs p, const Ragged rg) {
-  SSDK_DYN_SMEM(float, sm);
-  const int m = blockIdx.x, h0 = blockIdx.y * p.hg, nh = min(p.hg, p.H - h0);
-  const int s = rg.tok_seq[m], pos = rg.pos0[s] + (m - rg.cu[s]);
-  const int KR = p.kv_rank, R = p.R, W = KR + R, Wp = W | 1;
-  const int tid = threadIdx.x;
-  float* s_q = sm;
-  float* s_key = s_q + p.hg * W;
-  float* s_acc = s_key + kLatKC * Wp;
-  float* s_sc = s_acc + p.hg * KR;
-  float* s_m = s_sc + p.hg * kLatKC;
-  float* s_l = s_m + p.hg;
-  float* s_f = s_l + p.hg;
-  for (int e = tid; e < nh * W; e += kLatThreads) {
-    const int h = e / W, d = e % W;
-    s_q[e] = d < KR ? p.qlat[((size_t)m * p.H + h0 + h) * KR + d] : p.qr[((size_t)m * p.H + h0 + h) * R + (d - KR)];
+__global__ void latent_gather_kernel(const T* __restrict__ cache, T* __restrict__ keys, T* __restrict__ lat_t, const Ragged rg,
+                                     int s, int ctx, int ctx_pad, int KR, int W) {
+  const int j = blockIdx.x;
+  const T* row = j < ctx ? cache + page_row(rg, s, j) * (size_t)W : nullptr;
+  for (int d = threadIdx.x; d < W; d += blockDim.x) {
+    const float v = row ? ld_f<T>(row + d) : 0.f;
+    st_f<T>(keys + (size_t)j * W + d, v);
+    if (d < KR) st_f<T>(lat_t + (size_t)d * ctx_pad + j, v);
   }
-  for (int e = tid; e < nh * KR; e += kLatThreads) s_acc[e] = 0.f;
-  if (tid < nh) { s_m[tid] = ld_f<T>((const T*)p.sink + h0 + tid); s_l[tid] = 1.0f; }
-  const int ctx = pos + 1;
-  const int warp = tid >> 5, lane = tid & 31;
-  for (int c0 = 0; c0 < ctx; c0 += kLatKC) {
-    const int nk = min(kLatKC, ctx - c0);
-    __syncthreads();
-    for (int e = tid; e < nk * W; e += kLatThreads) {
-      const int jk = e / W, d = e % W;
-      s_key[jk * Wp + d] = ld_f<T>((const T*)p.cache + page_row(rg, s, c0 + jk) * (size_t)W + d);
-    }
-    __syncthreads();
-    for (int e = tid; e < nh * kLatKC; e += kLatThreads) {
-      const int h = e / kLatKC, jk = e % kLatKC;
-      float sc = -INFINITY;
-      if (jk < nk) {
-        float a = 0.f;
-        const float* qv = s_q + h * W;
-        const float* kv = s_key + jk * Wp;
-        for (int d = 0; d < W; ++d) a = fmaf(qv[d], kv[d], a);
-        sc = a * p.scale;
-      }
-      s_sc[e] = sc;
-    }
-    __syncthreads();
-    for (int h = warp; h < nh; h += kLatThreads / 32) {   // kLatKC == 32: one key per lane
-      const float sc = s_sc[h * kLatKC + lane];
-      const float mo = s_m[h], mn = fmaxf(mo, warp_max(sc));
-      const float pr = lane < nk ? expf(sc - mn) : 0.f;
-      const float sum = warp_sum(pr);
-      s_sc[h * kLatKC + lane] = pr;
-      if (lane == 0) {
-        const float f = expf(mo - mn);
-        s_f[h] = f;
-        s_l[h] = fmaf(s_l[h], f, sum);
-        s_m[h] = mn;
-      }
-    }
-    __syncthreads();
-    for (int e = tid; e < nh * KR; e += kLatThreads) {
-      const int h = e / KR, r = e % KR;
-      float a = s_acc[e] * s_f[h];
-      const float* pr = s_sc + h * kLatKC;
-      for (int jk = 0; jk < nk; ++jk) a = fmaf(pr[jk], s_key[jk * Wp + r], a);
-      s_acc[e] = a;
-    }
-  }
+}
+
+// Softmax with a sink over the score rows of one query block.  Row r = (query q0 + r / H, head r % H); the query at
+// position pos sees keys 0 .. pos.  sc [rows, ld] fp32 raw dot products -> pr [rows, ld] (T) weights, zero beyond pos and
+// in the padding.  The sink logit joins the maximum and adds exp(sink - max) to the denominator; it is not scaled.
+template <typename T>
+__global__ void sink_softmax_kernel(const float* __restrict__ sc, T* __restrict__ pr, const T* __restrict__ sink, int H, int ld,
+                                    int pos_first, float scale) {
+  __shared__ float red[33];
+  const int r = blockIdx.x, h = r % H, n = pos_first + r / H + 1;  // keys this row sees
+  const float* srow = sc + (size_t)r * ld;
+  const float sk = ld_f<T>(sink + h);
+  float mx = sk;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) mx = fmaxf(mx, srow[j] * scale);
   __syncthreads();
-  for (int e = tid; e < nh * KR; e += kLatThreads) {
-    const int h = e / KR, r = e % KR;
-    st_f<T>((T*)p.out + ((size_t)m * p.H + h0 + h) * KR + r, s_acc[e] / s_l[h]);
-  }
+  mx = warp_max(mx);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = red[0];
+  for (int w = 1; w < (int)(blockDim.x >> 5); ++w) mx = fmaxf(mx, red[w]);
+  float sum = 0.f;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) sum += expf(srow[j] * scale - mx);
+  sum = block_sum(sum, red) + expf(sk - mx);
+  const float inv = 1.0f / sum;
+  for (int j = threadIdx.x; j < ld; j += blockDim.x) st_f<T>(pr + (size_t)r * ld + j, j < n ? expf(srow[j] * scale - mx) * inv : 0.f);
 }
 
 }  // namespace ssdk

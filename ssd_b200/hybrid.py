@@ -193,6 +193,47 @@ def load_hybrid_weights(path: str, spec: HybridSpec, dtype: torch.dtype, device)
     return pack_hybrid_weights(spec, read_safetensors(os.path.join(path, "model.safetensors")), dtype, device)
 
 
+def random_hybrid_weights(spec: HybridSpec, dtype: torch.dtype, device, seed: int = 0) -> dict:
+    """Random weights in the packed layout, generated on the device (benchmarks: there are no checkpoints to load).
+    Scales keep activations O(1): linear layers N(0, 1/in), norm offsets small, decays spread over (0.2, 0.9)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    W = spec.width
+
+    def lin(*shape):
+        return (torch.randn(*shape, generator=g, device=device) / shape[-1] ** 0.5).to(dtype)
+
+    def vec(n, mean=0.0, std=0.1):
+        return (mean + std * torch.randn(n, generator=g, device=device)).to(dtype)
+
+    w = {"EMBED": torch.randn(spec.vocab, W, generator=g, device=device).to(dtype), "HEAD": lin(spec.vocab, W),
+         "FINAL_NORM": vec(W), "layers": []}
+    for ls in spec.layers:
+        H, D, V = ls.heads, ls.dim, ls.vdim
+        lw = {"NORM": vec(W), "LS_MIX": vec(W, 1.0), "MIX_OUT": lin(W, H * V)}
+        if ls.mixer == "wkv":
+            lw["WKV_MU"] = torch.rand(5, W, generator=g, device=device).to(dtype)
+            for s_ in "RKVG":
+                lw["WKV_" + s_] = lin(H * D, W)
+            lw["WKV_W1"], lw["WKV_W2"] = lin(ls.decay_rank, W), lin(H * D, ls.decay_rank)
+            lw["WKV_W0"] = (torch.rand(H * D, generator=g, device=device) * 3.0 - 2.5).to(dtype)
+            lw["WKV_U"], lw["MIX_NORM"] = vec(H * D, 0.0, 0.5).view(H, D), vec(H * D, 1.0)
+        elif ls.mixer == "mlstm":
+            lw["MLSTM_IN"] = lin(2 * H * D + 2 * H * V + 2 * H, W)
+            lw["MLSTM_IB"], lw["MLSTM_FB"], lw["MIX_NORM"] = vec(H, 0.0, 1.0), vec(H, 2.5, 0.5), vec(H * V, 1.0)
+        else:
+            lw["LAT_DOWN"] = lin(ls.q_rank + ls.kv_rank + ls.rot_dim, W)
+            lw["LAT_QNORM"], lw["LAT_KVNORM"] = vec(ls.q_rank, 1.0), vec(ls.kv_rank, 1.0)
+            lw["LAT_UQ"], lw["LAT_UV"] = lin(H * (D + ls.rot_dim), ls.q_rank), lin(H * V, ls.kv_rank)
+            lw["LAT_UKT"], lw["LAT_SINK"] = (lin(H, ls.kv_rank, D) * (D / ls.kv_rank) ** 0.5).contiguous(), vec(H, 0.0, 1.0)
+        if ls.mlp == "moe":
+            lw["LS_MLP"], lw["ROUTER"] = vec(W, 1.0), lin(ls.experts, W)
+            lw["EXPERT_IN"], lw["EXPERT_OUT"] = lin(ls.experts, 2 * ls.ff, W), lin(ls.experts, W, ls.ff)
+            if ls.shared_ff:
+                lw["SHARED_IN"], lw["SHARED_OUT"] = lin(2 * ls.shared_ff + 1, W), lin(W, ls.shared_ff)
+        w["layers"].append(lw)
+    return w
+
+
 def _i32(a):
     return np.ascontiguousarray(a, dtype=np.int32)
 
