@@ -77,13 +77,13 @@ static int hyb_derive(ssdk_hyb_engine* e) {
     if (H < 1 || D < 1) return fail("hybrid layer: heads / dim must be positive");
     L.state_off = soff;
     if (c.mixer == SSDK_MIX_WKV) {
-      if (D > 1024 || (size_t)(D * D + 5 * D) * 4 > 200 * 1024) return fail("wkv: head dim %d too large for the resident-state scan", D);
+      if (D > 1024 || (size_t)(D * D + 5 * D + 1024) * 4 > 200 * 1024) return fail("wkv: head dim %d too large for the resident-state scan", D);
       soff += (size_t)H * D * D + g.width;
       up(e->w_p0, 5LL * H * D); up(e->w_p1, c.decay_rank); up(e->w_p2, (long long)H * D);
       up(e->w_t0, c.decay_rank); up(e->w_t1, (long long)H * D);
       e->any_wkv = true;
     } else if (c.mixer == SSDK_MIX_MLSTM) {
-      if (V < 1 || std::max(D, V) > 1024 || (size_t)(D * V + 3 * D) * 4 > 200 * 1024) return fail("mlstm: head sizes %d x %d too large", D, V);
+      if (V < 1 || std::max(D, V) > 1024 || (size_t)(D * V + 3 * D + 1024) * 4 > 200 * 1024) return fail("mlstm: head sizes %d x %d too large", D, V);
       soff += (size_t)H * D * V + (size_t)H * D + H;
       up(e->w_p0, 2LL * H * D + 2LL * H * V + 2 * H); up(e->w_p2, (long long)H * V); up(e->w_t1, (long long)H * V);
     } else if (c.mixer == SSDK_MIX_LATENT_ATTN) {
@@ -233,6 +233,15 @@ struct HybRun {
     return 0;
   }
 
+  // scan CTA: V columns (padded to a warp) x G row groups of >= 8 rows, at most 512 threads
+  static ssdk::ScanShape scan_shape(int D, int V) {
+    ssdk::ScanShape sh;
+    sh.Vr = (V + 31) / 32 * 32;
+    sh.G = std::max(1, std::min({8, 512 / sh.Vr, D / 8}));
+    sh.Dg = (D + sh.G - 1) / sh.G;
+    return sh;
+  }
+
   int wkv(HybLayer& Lr) {
     const ssdk_hyb_layer_cfg& c = Lr.c;
     const int H = c.heads, D = c.dim, HD = H * D, W = e->cfg.width;
@@ -265,8 +274,9 @@ struct HybRun {
     ssdk::WkvArgs a;
     a.r = pr; a.k = pk; a.v = pv; a.zw = pw; a.ld = HD; a.w0 = Lr.t[SSDK_HT_WKV_W0].p; a.u = Lr.t[SSDK_HT_WKV_U].p;
     a.o = e->p2; a.state = st; a.slot_stride = e->slot_floats; a.h = e->h; a.h_prev = h_prev; a.width = W; a.H = H; a.D = D;
-    const size_t smem = (size_t)(D * D + 5 * D) * 4;
-    CKI(L.go(ssdk::wkv_scan_kernel<T>, dim3(rg.n_seqs, H), dim3((D + 31) / 32 * 32), smem, a, rg));
+    const ssdk::ScanShape sh = scan_shape(D, D);
+    const size_t smem = (size_t)(D * D + 5 * D + sh.G * sh.Vr) * 4;
+    CKI(L.go(ssdk::wkv_scan_kernel<T>, dim3(rg.n_seqs, H), dim3(sh.Vr * sh.G), smem, a, rg, sh));
     CKI(L.go(ssdk::head_rmsnorm_gate_kernel<T, 0>, dim3(M, H), dim3(std::min(256, (D + 31) / 32 * 32)), 0, (const float*)e->p2,
              (const float*)pg, HD, (const T*)Lr.t[SSDK_HT_MIX_NORM].p, (T*)e->t1, H, D, e->cfg.eps));
     return lin(e->t1, HD, Lr.t[SSDK_HT_MIX_OUT].p, HD, e->mix_out, W, M, W, HD);
@@ -288,8 +298,9 @@ struct HybRun {
     float* st = e->state + Lr.state_off;
     a.S = st; a.n = st + (size_t)H * D * V; a.m = a.n + (size_t)H * D; a.slot_stride = e->slot_floats;
     a.H = H; a.D = D; a.V = V; a.cap = c.gate_cap; a.q_scale = 1.0f / sqrtf((float)D);
-    const size_t smem = (size_t)(D * V + 3 * D) * 4;
-    CKI(L.go(ssdk::mlstm_scan_kernel<T>, dim3(rg.n_seqs, H), dim3((std::max(D, V) + 31) / 32 * 32), smem, a, rg));
+    const ssdk::ScanShape sh = scan_shape(D, V);
+    const size_t smem = (size_t)(D * V + 3 * D + sh.G * sh.Vr + sh.G) * 4;
+    CKI(L.go(ssdk::mlstm_scan_kernel<T>, dim3(rg.n_seqs, H), dim3(sh.Vr * sh.G), smem, a, rg, sh));
     CKI(L.go(ssdk::head_rmsnorm_gate_kernel<T, 1>, dim3(M, H), dim3(std::min(256, (V + 31) / 32 * 32)), 0, (const float*)e->p2, g, N,
              (const T*)Lr.t[SSDK_HT_MIX_NORM].p, (T*)e->t1, H, V, e->cfg.eps));
     return lin(e->t1, H * V, Lr.t[SSDK_HT_MIX_OUT].p, H * V, e->mix_out, W, M, W, H * V);

@@ -1,7 +1,7 @@
 // recurrent.cuh — matrix-state recurrences of the layered (hybrid) models.  One CTA per (sequence, head) walks the
 // rows that this step brings for the sequence, in order, with the head's state matrix S [K, V] resident in shared
-// memory (thread j owns column j: S[i][j] at s_S[i * V + j], so a warp's accesses are conflict free) and writes it
-// back to the sequence's state slot.  Everything that enters the recurrence (decays, gates, stabiliser, state, the
+// memory (a thread owns a run of rows of ONE column: S[i][j] at s_S[i * V + j], so a warp's accesses are conflict
+// free) and writes it back to the sequence's state slot.  Everything that enters the recurrence (decays, gates, stabiliser, state, the
 // read-out) is fp32; the projections arrive as fp32 GEMM outputs.
 //
 //   wkv_scan_kernel   (RWKV-style, per-channel data-dependent decay, bonus u for the current token)
@@ -29,52 +29,81 @@ struct WkvArgs {
   int H, D;
 };
 
+// Thread layout of both scans: tid = g * Vr + j, Vr = V rounded up to a warp: column j of the state, row group g of G
+// (rows [g * Dg, (g + 1) * Dg)).  The G partial read-outs of a column meet in shared memory and are summed in the
+// fixed order g = 0 .. G-1.  The next row's operands are requested from global memory before the current row's
+// arithmetic starts, so their latency hides behind it.
+struct ScanShape {
+  int Vr, G, Dg;
+};
+
 template <typename T>
-__global__ void wkv_scan_kernel(const WkvArgs p, const Ragged rg) {
+__global__ void wkv_scan_kernel(const WkvArgs p, const Ragged rg, const ScanShape sh) {
   SSDK_DYN_SMEM(float, sm);
-  const int s = blockIdx.x, hd = blockIdx.y, D = p.D, j = threadIdx.x;
+  const int s = blockIdx.x, hd = blockIdx.y, D = p.D, tid = threadIdx.x, nt = blockDim.x;
+  const int j = tid % sh.Vr, g = tid / sh.Vr, i_lo = g * sh.Dg, i_hi = min(D, i_lo + sh.Dg);
   float* s_S = sm;            // [D][D]
   float* s_r = s_S + D * D;   // [D]
   float* s_k = s_r + D;
   float* s_w = s_k + D;
   float* s_u = s_w + D;
   float* s_w0 = s_u + D;
+  float* s_part = s_w0 + D;   // [G][Vr]
   const int row_lo = rg.cu[s], row_hi = rg.cu[s + 1];
   if (row_hi <= row_lo) return;
   float* S_g = p.state + (size_t)rg.slot[s] * p.slot_stride + (size_t)hd * D * D;
   const bool fresh = rg.pos0[s] == 0;
-  for (int e = j; e < D * D; e += blockDim.x) s_S[e] = fresh ? 0.f : S_g[e];
-  if (j < D) {
-    s_u[j] = ld_f<T>((const T*)p.u + hd * D + j);
-    s_w0[j] = ld_f<T>((const T*)p.w0 + hd * D + j);
+  for (int e = tid; e < D * D; e += nt) s_S[e] = fresh ? 0.f : S_g[e];
+  for (int e = tid; e < D; e += nt) {
+    s_u[e] = ld_f<T>((const T*)p.u + hd * D + e);
+    s_w0[e] = ld_f<T>((const T*)p.w0 + hd * D + e);
+  }
+  // prefetched operands of the coming row: element `tid` of r, k, z (threads below D) and v[j]
+  float nr = 0.f, nk = 0.f, nz = 0.f, nv = 0.f;
+  {
+    const size_t base = (size_t)row_lo * p.ld + hd * D;
+    if (tid < D) { nr = p.r[base + tid]; nk = p.k[base + tid]; nz = p.zw[base + tid]; }
+    if (j < D) nv = p.v[base + j];
   }
   for (int t = row_lo; t < row_hi; ++t) {
     __syncthreads();
     const size_t base = (size_t)t * p.ld + hd * D;
-    float vj = 0.f;
-    if (j < D) {
-      s_r[j] = p.r[base + j];
-      s_k[j] = p.k[base + j];
-      s_w[j] = expf(-expf(p.zw[base + j] + s_w0[j]));
-      vj = p.v[base + j];
+    if (tid < D) { s_r[tid] = nr; s_k[tid] = nk; s_w[tid] = expf(-expf(nz + s_w0[tid])); }
+    for (int e = tid + nt; e < D; e += nt) {   // heads wider than the CTA
+      s_r[e] = p.r[base + e]; s_k[e] = p.k[base + e]; s_w[e] = expf(-expf(p.zw[base + e] + s_w0[e]));
     }
+    const float vj = nv;
     __syncthreads();
+    if (t + 1 < row_hi) {
+      const size_t nb = base + p.ld;
+      if (tid < D) { nr = p.r[nb + tid]; nk = p.k[nb + tid]; nz = p.zw[nb + tid]; }
+      if (j < D) nv = p.v[nb + j];
+    }
+    float acc = 0.f;
     if (j < D) {
-      float acc = 0.f;
-      for (int i = 0; i < D; ++i) {
+#pragma unroll 4
+      for (int i = i_lo; i < i_hi; ++i) {
         const float st = s_S[i * D + j];
         const float kv = s_k[i] * vj;
         acc = fmaf(s_r[i], fmaf(s_u[i], kv, st), acc);
         s_S[i * D + j] = fmaf(s_w[i], st, kv);
       }
-      p.o[(size_t)t * p.H * D + hd * D + j] = acc;
     }
+    if (sh.G > 1) {
+      s_part[g * sh.Vr + j] = acc;
+      __syncthreads();
+      if (g == 0) {
+        acc = s_part[j];
+        for (int q = 1; q < sh.G; ++q) acc += s_part[q * sh.Vr + j];
+      }
+    }
+    if (g == 0 && j < D) p.o[(size_t)t * p.H * D + hd * D + j] = acc;
   }
   __syncthreads();
-  for (int e = j; e < D * D; e += blockDim.x) S_g[e] = s_S[e];
+  for (int e = tid; e < D * D; e += nt) S_g[e] = s_S[e];
   if (hd == 0) {
     float* hp = p.h_prev + (size_t)rg.slot[s] * p.slot_stride;
-    for (int c = j; c < p.width; c += blockDim.x) hp[c] = ld_f<T>((const T*)p.h + (size_t)(row_hi - 1) * p.width + c);
+    for (int c = tid; c < p.width; c += nt) hp[c] = ld_f<T>((const T*)p.h + (size_t)(row_hi - 1) * p.width + c);
   }
 }
 
@@ -93,13 +122,16 @@ struct MlstmArgs {
 SSDK_DEVINL float log_sigmoid_f(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
 template <typename T>
-__global__ void mlstm_scan_kernel(const MlstmArgs p, const Ragged rg) {
+__global__ void mlstm_scan_kernel(const MlstmArgs p, const Ragged rg, const ScanShape sh) {
   SSDK_DYN_SMEM(float, sm);
-  const int s = blockIdx.x, hd = blockIdx.y, D = p.D, V = p.V, j = threadIdx.x;
+  const int s = blockIdx.x, hd = blockIdx.y, D = p.D, V = p.V, tid = threadIdx.x, nt = blockDim.x;
+  const int j = tid % sh.Vr, g = tid / sh.Vr, i_lo = g * sh.Dg, i_hi = min(D, i_lo + sh.Dg);
   float* s_S = sm;            // [D][V]
   float* s_q = s_S + D * V;   // [D]
   float* s_k = s_q + D;
   float* s_n = s_k + D;
+  float* s_part = s_n + D;    // [G][Vr] read-out partials
+  float* s_dot = s_part + sh.G * sh.Vr;  // [G] partial n . q
   const int row_lo = rg.cu[s], row_hi = rg.cu[s + 1];
   if (row_hi <= row_lo) return;
   const size_t slot = (size_t)rg.slot[s] * p.slot_stride;
@@ -107,42 +139,65 @@ __global__ void mlstm_scan_kernel(const MlstmArgs p, const Ragged rg) {
   float* n_g = p.n + slot + (size_t)hd * D;
   float* m_g = p.m + slot + hd;
   const bool fresh = rg.pos0[s] == 0;
-  for (int e = j; e < D * V; e += blockDim.x) s_S[e] = fresh ? 0.f : S_g[e];
-  for (int e = j; e < D; e += blockDim.x) s_n[e] = fresh ? 0.f : n_g[e];
+  for (int e = tid; e < D * V; e += nt) s_S[e] = fresh ? 0.f : S_g[e];
+  for (int e = tid; e < D; e += nt) s_n[e] = fresh ? 0.f : n_g[e];
   float m = fresh ? 0.f : *m_g;
   const float ib = ld_f<T>((const T*)p.ib + hd), fb = ld_f<T>((const T*)p.fb + hd);
+  float nq = 0.f, nk = 0.f, nv = 0.f, ni, nf;
+  {
+    const size_t base = (size_t)row_lo * p.ld;
+    if (tid < D) { nq = p.q[base + hd * D + tid]; nk = p.k[base + hd * D + tid]; }
+    if (j < V) nv = p.v[base + hd * V + j];
+    ni = p.ig[base + hd]; nf = p.fg[base + hd];
+  }
   for (int t = row_lo; t < row_hi; ++t) {
-    const float iraw = p.ig[(size_t)t * p.ld + hd] + ib, fraw = p.fg[(size_t)t * p.ld + hd] + fb;
-    const float ig = p.cap * tanhf(iraw / p.cap);
-    const float fg = log_sigmoid_f(p.cap * tanhf(fraw / p.cap));
+    const size_t base = (size_t)t * p.ld;
+    const float ig = p.cap * tanhf((ni + ib) / p.cap);
+    const float fg = log_sigmoid_f(p.cap * tanhf((nf + fb) / p.cap));
     const float mn = fmaxf(fg + m, ig);
     const float a = expf(fg + m - mn), b = expf(ig - mn);
     m = mn;
-    __syncthreads();  // the previous row's readers of s_q / s_k / s_n are done
-    for (int e = j; e < D; e += blockDim.x) {
-      const float kk = p.k[(size_t)t * p.ld + hd * D + e];
-      s_q[e] = p.q[(size_t)t * p.ld + hd * D + e] * p.q_scale;
-      s_k[e] = kk;
-      s_n[e] = fmaf(a, s_n[e], b * kk);
+    __syncthreads();  // the previous row's readers of s_q / s_k / s_n / s_part are done
+    if (tid < D) { s_q[tid] = nq * p.q_scale; s_k[tid] = nk; s_n[tid] = fmaf(a, s_n[tid], b * nk); }
+    for (int e = tid + nt; e < D; e += nt) {   // heads wider than the CTA
+      const float kk = p.k[base + hd * D + e];
+      s_q[e] = p.q[base + hd * D + e] * p.q_scale; s_k[e] = kk; s_n[e] = fmaf(a, s_n[e], b * kk);
     }
+    const float bv = b * nv;
     __syncthreads();
+    if (t + 1 < row_hi) {
+      const size_t nb = base + p.ld;
+      if (tid < D) { nq = p.q[nb + hd * D + tid]; nk = p.k[nb + hd * D + tid]; }
+      if (j < V) nv = p.v[nb + hd * V + j];
+      ni = p.ig[nb + hd]; nf = p.fg[nb + hd];
+    }
+    float acc = 0.f, dot = 0.f;
     if (j < V) {
-      const float bv = b * p.v[(size_t)t * p.ld + hd * V + j];
-      float acc = 0.f, dot = 0.f;
-      for (int i = 0; i < D; ++i) {
+#pragma unroll 4
+      for (int i = i_lo; i < i_hi; ++i) {
         const float st = fmaf(a, s_S[i * V + j], s_k[i] * bv);
         s_S[i * V + j] = st;
         acc = fmaf(st, s_q[i], acc);
-        dot = fmaf(s_n[i], s_q[i], dot);
       }
+    }
+    if (j == 0) {
+      for (int i = i_lo; i < i_hi; ++i) dot = fmaf(s_n[i], s_q[i], dot);
+      s_dot[g] = dot;
+    }
+    s_part[g * sh.Vr + j] = acc;
+    __syncthreads();
+    if (g == 0 && j < V) {
+      acc = s_part[j];
+      dot = s_dot[0];
+      for (int q = 1; q < sh.G; ++q) { acc += s_part[q * sh.Vr + j]; dot += s_dot[q]; }
       const float den = fmaxf(fabsf(dot), expf(-m)) + 1e-6f;
       p.o[(size_t)t * p.H * V + hd * V + j] = acc / den;
     }
   }
   __syncthreads();
-  for (int e = j; e < D * V; e += blockDim.x) S_g[e] = s_S[e];
-  for (int e = j; e < D; e += blockDim.x) n_g[e] = s_n[e];
-  if (j == 0) *m_g = m;
+  for (int e = tid; e < D * V; e += nt) S_g[e] = s_S[e];
+  for (int e = tid; e < D; e += nt) n_g[e] = s_n[e];
+  if (tid == 0) *m_g = m;
 }
 
 }  // namespace ssdk
