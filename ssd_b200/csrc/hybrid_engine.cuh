@@ -242,6 +242,19 @@ struct HybRun {
     return sh;
   }
 
+  // register-resident scan: the fewest rows per thread (8, 16 or 32) whose row groups fit 512 threads; *dg = 0 if none
+  static ssdk::ScanShape reg_scan_shape(int D, int V, int* dg) {
+    ssdk::ScanShape sh;
+    sh.Vr = (V + 31) / 32 * 32;
+    *dg = 0;
+    if (env_int("SSDK_HYB_SCAN_SMEM", 0)) return sh;
+    for (int d : {8, 16, 32}) {
+      const int G = (D + d - 1) / d;
+      if (sh.Vr * G <= 512) { *dg = d; sh.G = G; sh.Dg = d; break; }
+    }
+    return sh;
+  }
+
   int wkv(HybLayer& Lr) {
     const ssdk_hyb_layer_cfg& c = Lr.c;
     const int H = c.heads, D = c.dim, HD = H * D, W = e->cfg.width;
@@ -274,9 +287,19 @@ struct HybRun {
     ssdk::WkvArgs a;
     a.r = pr; a.k = pk; a.v = pv; a.zw = pw; a.ld = HD; a.w0 = Lr.t[SSDK_HT_WKV_W0].p; a.u = Lr.t[SSDK_HT_WKV_U].p;
     a.o = e->p2; a.state = st; a.slot_stride = e->slot_floats; a.h = e->h; a.h_prev = h_prev; a.width = W; a.H = H; a.D = D;
-    const ssdk::ScanShape sh = scan_shape(D, D);
-    const size_t smem = (size_t)(D * D + 5 * D + sh.G * sh.Vr) * 4;
-    CKI(L.go(ssdk::wkv_scan_kernel<T>, dim3(rg.n_seqs, H), dim3(sh.Vr * sh.G), smem, a, rg, sh));
+    int dg = 0;
+    ssdk::ScanShape sh = reg_scan_shape(D, D, &dg);
+    if (dg) {
+      const size_t smem = (size_t)sh.G * dg * 16 + (size_t)sh.G * sh.Vr * 4;
+      const dim3 grid(rg.n_seqs, H), block(sh.Vr * sh.G);
+      if (dg == 8) CKI(L.go(ssdk::wkv_scan_reg_kernel<T, 8>, grid, block, smem, a, rg, sh));
+      else if (dg == 16) CKI(L.go(ssdk::wkv_scan_reg_kernel<T, 16>, grid, block, smem, a, rg, sh));
+      else CKI(L.go(ssdk::wkv_scan_reg_kernel<T, 32>, grid, block, smem, a, rg, sh));
+    } else {
+      sh = scan_shape(D, D);
+      const size_t smem = (size_t)(D * D + 5 * D + sh.G * sh.Vr) * 4;
+      CKI(L.go(ssdk::wkv_scan_kernel<T>, dim3(rg.n_seqs, H), dim3(sh.Vr * sh.G), smem, a, rg, sh));
+    }
     CKI(L.go(ssdk::head_rmsnorm_gate_kernel<T, 0>, dim3(M, H), dim3(std::min(256, (D + 31) / 32 * 32)), 0, (const float*)e->p2,
              (const float*)pg, HD, (const T*)Lr.t[SSDK_HT_MIX_NORM].p, (T*)e->t1, H, D, e->cfg.eps));
     return lin(e->t1, HD, Lr.t[SSDK_HT_MIX_OUT].p, HD, e->mix_out, W, M, W, HD);
@@ -298,9 +321,19 @@ struct HybRun {
     float* st = e->state + Lr.state_off;
     a.S = st; a.n = st + (size_t)H * D * V; a.m = a.n + (size_t)H * D; a.slot_stride = e->slot_floats;
     a.H = H; a.D = D; a.V = V; a.cap = c.gate_cap; a.q_scale = 1.0f / sqrtf((float)D);
-    const ssdk::ScanShape sh = scan_shape(D, V);
-    const size_t smem = (size_t)(D * V + 3 * D + sh.G * sh.Vr + sh.G) * 4;
-    CKI(L.go(ssdk::mlstm_scan_kernel<T>, dim3(rg.n_seqs, H), dim3(sh.Vr * sh.G), smem, a, rg, sh));
+    int dg = 0;
+    ssdk::ScanShape sh = reg_scan_shape(D, V, &dg);
+    if (dg) {
+      const size_t smem = (size_t)sh.G * dg * 12 + (size_t)(sh.G * sh.Vr + sh.G) * 4;
+      const dim3 grid(rg.n_seqs, H), block(sh.Vr * sh.G);
+      if (dg == 8) CKI(L.go(ssdk::mlstm_scan_reg_kernel<T, 8>, grid, block, smem, a, rg, sh));
+      else if (dg == 16) CKI(L.go(ssdk::mlstm_scan_reg_kernel<T, 16>, grid, block, smem, a, rg, sh));
+      else CKI(L.go(ssdk::mlstm_scan_reg_kernel<T, 32>, grid, block, smem, a, rg, sh));
+    } else {
+      sh = scan_shape(D, V);
+      const size_t smem = (size_t)(D * V + 3 * D + sh.G * sh.Vr + sh.G) * 4;
+      CKI(L.go(ssdk::mlstm_scan_kernel<T>, dim3(rg.n_seqs, H), dim3(sh.Vr * sh.G), smem, a, rg, sh));
+    }
     CKI(L.go(ssdk::head_rmsnorm_gate_kernel<T, 1>, dim3(M, H), dim3(std::min(256, (V + 31) / 32 * 32)), 0, (const float*)e->p2, g, N,
              (const T*)Lr.t[SSDK_HT_MIX_NORM].p, (T*)e->t1, H, V, e->cfg.eps));
     return lin(e->t1, H * V, Lr.t[SSDK_HT_MIX_OUT].p, H * V, e->mix_out, W, M, W, H * V);

@@ -120,16 +120,17 @@ __global__ void __launch_bounds__(kLinThreads) linear_kernel(const LinearArgs p)
 }
 
 // Tensor-core tile for bf16 (legacy mma.sync path; operands need 16-byte aligned rows: K, lda, ldw and the batch strides
-// multiples of 8).  64 x 64 outputs per CTA, four warps of 32 x 32, k-steps of 32 staged through padded shared memory
-// (row stride 80 B: ldmatrix rows fall into distinct 16-byte bank groups) with the next step's global loads in
-// registers while the current one is multiplied.
-constexpr int kMmaThreads = 128, kMmaBK = 32, kMmaLd = kMmaBK + 8;
+// multiples of 8).  64 x 64 outputs per CTA, four warps of 32 x 32, k-steps of 32 through a three-stage cp.async ring of
+// padded shared-memory tiles (row stride 80 B: ldmatrix rows fall into distinct 16-byte bank groups): two k-steps of
+// global loads are in flight under the one being multiplied, which is what a few-row (decode) call needs to stream
+// weights and what a prefill call needs to hide latency.  One __syncthreads per k-step.
+constexpr int kMmaThreads = 128, kMmaBK = 32, kMmaLd = kMmaBK + 8, kMmaStages = 3;
 
 template <typename OutT>
 __global__ void __launch_bounds__(kMmaThreads) linear_mma_kernel(const LinearArgs p) {
   typedef __nv_bfloat16 T;
-  __shared__ __align__(16) T As[kLinBM][kMmaLd];
-  __shared__ __align__(16) T Ws[kLinBN][kMmaLd];
+  __shared__ __align__(16) T As[kMmaStages][kLinBM][kMmaLd];
+  __shared__ __align__(16) T Ws[kMmaStages][kLinBN][kMmaLd];
   int row0, nrows;
   const T* W = (const T*)p.W + (long long)blockIdx.z * p.sW;
   const T* A = (const T*)p.A + (long long)blockIdx.z * p.sA;
@@ -146,7 +147,7 @@ __global__ void __launch_bounds__(kMmaThreads) linear_mma_kernel(const LinearArg
   }
   const int col0 = blockIdx.x * kLinBN;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, wm = warp >> 1, wn = warp & 1;
-  // staging: vector v = tid + i * 128 -> row v / 4, k offset (v % 4) * 8
+  // staging: vector v = tid + i * 128 -> row v / 4, k offset (v % 4) * 8; a row outside the tile is zero-filled
   const T* a_src[2];
   const T* w_src[2];
 #pragma unroll
@@ -165,40 +166,41 @@ __global__ void __launch_bounds__(kMmaThreads) linear_mma_kernel(const LinearArg
     for (int j = 0; j < 4; ++j)
 #pragma unroll
       for (int k = 0; k < 4; ++k) acc[i][j][k] = 0.f;
-  uint4 ra[2], rw[2];
-  auto fetch = [&](int k0) {
+  const int nk = (p.K + kMmaBK - 1) / kMmaBK;
+  auto issue = [&](int kt) {
+    if (kt < nk) {
+      const int k0 = kt * kMmaBK, st = kt % kMmaStages;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int kv = ((tid + i * kMmaThreads) & 3) * 8;
-      const bool kin = k0 + kv < p.K;
-      ra[i] = (a_src[i] && kin) ? *reinterpret_cast<const uint4*>(a_src[i] + k0) : make_uint4(0, 0, 0, 0);
-      rw[i] = (w_src[i] && kin) ? ld_nc_v4(w_src[i] + k0) : make_uint4(0, 0, 0, 0);
+      for (int i = 0; i < 2; ++i) {
+        const int v = tid + i * kMmaThreads, r = v >> 2, kv = (v & 3) * 8;
+        const bool kin = k0 + kv < p.K;
+        const bool av = a_src[i] && kin, wv = w_src[i] && kin;
+        cp_async16(&As[st][r][kv], av ? (const void*)(a_src[i] + k0) : (const void*)A, av);
+        cp_async16(&Ws[st][r][kv], wv ? (const void*)(w_src[i] + k0) : (const void*)W, wv);
+      }
     }
+    cp_async_commit();
   };
-  fetch(0);
-  for (int k0 = 0; k0 < p.K; k0 += kMmaBK) {
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int v = tid + i * kMmaThreads, r = v >> 2, kv = (v & 3) * 8;
-      *reinterpret_cast<uint4*>(&As[r][kv]) = ra[i];
-      *reinterpret_cast<uint4*>(&Ws[r][kv]) = rw[i];
-    }
+  issue(0);
+  issue(1);
+  for (int kt = 0; kt < nk; ++kt) {
+    cp_async_wait<1>();
     __syncthreads();
-    if (k0 + kMmaBK < p.K) fetch(k0 + kMmaBK);
+    issue(kt + 2);
+    const int st = kt % kMmaStages;
 #pragma unroll
     for (int kk = 0; kk < kMmaBK; kk += 16) {
       uint32_t a[2][4], b[2][4];
 #pragma unroll
-      for (int mi = 0; mi < 2; ++mi) ldmatrix_x4(a[mi], &As[wm * 32 + mi * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+      for (int mi = 0; mi < 2; ++mi) ldmatrix_x4(a[mi], &As[st][wm * 32 + mi * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
 #pragma unroll
       for (int nj = 0; nj < 2; ++nj)
-        ldmatrix_x4(b[nj], &Ws[wn * 32 + nj * 16 + (lane >> 4) * 8 + (lane & 7)][kk + ((lane >> 3) & 1) * 8]);
+        ldmatrix_x4(b[nj], &Ws[st][wn * 32 + nj * 16 + (lane >> 4) * 8 + (lane & 7)][kk + ((lane >> 3) & 1) * 8]);
 #pragma unroll
       for (int mi = 0; mi < 2; ++mi)
 #pragma unroll
         for (int ni = 0; ni < 4; ++ni) mma_bf16_16816(acc[mi][ni], a[mi], b[ni >> 1][(ni & 1) * 2], b[ni >> 1][(ni & 1) * 2 + 1]);
     }
-    __syncthreads();
   }
   const int g = lane >> 2, t = lane & 3;
 #pragma unroll

@@ -107,6 +107,69 @@ __global__ void wkv_scan_kernel(const WkvArgs p, const Ragged rg, const ScanShap
   }
 }
 
+// Register-resident variant: every thread keeps its DG rows of its column in registers for the whole portion (the state
+// never touches shared memory), the per-row operands {r, k, w, u} travel as ONE float4 per state row (rows beyond the
+// head size are zero operands), so a state row costs one broadcast shared-memory load instead of six accesses.
+// Launched when G * DG >= D with DG in {8, 16, 32} fits a CTA; the shared-memory kernel above serves every other size.
+template <typename T, int DG>
+__global__ void __launch_bounds__(512) wkv_scan_reg_kernel(const WkvArgs p, const Ragged rg, const ScanShape sh) {
+  SSDK_DYN_SMEM(float4, sm4);
+  const int s = blockIdx.x, hd = blockIdx.y, D = p.D, tid = threadIdx.x;
+  const int j = tid % sh.Vr, g = tid / sh.Vr, i_lo = g * DG, rows = sh.G * DG;
+  float4* s_op = sm4;                                        // [rows] {r, k, w, u}
+  float* s_part = reinterpret_cast<float*>(s_op + rows);     // [G][Vr]
+  const int row_lo = rg.cu[s], row_hi = rg.cu[s + 1];
+  if (row_hi <= row_lo) return;
+  float* S_g = p.state + (size_t)rg.slot[s] * p.slot_stride + (size_t)hd * D * D;
+  const bool fresh = rg.pos0[s] == 0;
+  float S[DG];
+#pragma unroll
+  for (int ii = 0; ii < DG; ++ii) S[ii] = (!fresh && j < D && i_lo + ii < D) ? S_g[(size_t)(i_lo + ii) * D + j] : 0.f;
+  float my_u = 0.f, my_w0 = 0.f;
+  if (tid < D) { my_u = ld_f<T>((const T*)p.u + hd * D + tid); my_w0 = ld_f<T>((const T*)p.w0 + hd * D + tid); }
+  float nr = 0.f, nk = 0.f, nz = 0.f, nv = 0.f;
+  {
+    const size_t base = (size_t)row_lo * p.ld + hd * D;
+    if (tid < D) { nr = p.r[base + tid]; nk = p.k[base + tid]; nz = p.zw[base + tid]; }
+    if (j < D) nv = p.v[base + j];
+  }
+  for (int t = row_lo; t < row_hi; ++t) {
+    __syncthreads();
+    if (tid < rows) s_op[tid] = tid < D ? make_float4(nr, nk, expf(-expf(nz + my_w0)), my_u) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float vj = nv;
+    __syncthreads();
+    if (t + 1 < row_hi) {
+      const size_t nb = (size_t)(t + 1) * p.ld + hd * D;
+      if (tid < D) { nr = p.r[nb + tid]; nk = p.k[nb + tid]; nz = p.zw[nb + tid]; }
+      if (j < D) nv = p.v[nb + j];
+    }
+    float acc = 0.f;
+#pragma unroll
+    for (int ii = 0; ii < DG; ++ii) {
+      const float4 o = s_op[i_lo + ii];
+      const float kv = o.y * vj;
+      acc = fmaf(o.x, fmaf(o.w, kv, S[ii]), acc);
+      S[ii] = fmaf(o.z, S[ii], kv);
+    }
+    if (sh.G > 1) {
+      s_part[g * sh.Vr + j] = acc;
+      __syncthreads();
+      if (g == 0) {
+        acc = s_part[j];
+        for (int q = 1; q < sh.G; ++q) acc += s_part[q * sh.Vr + j];
+      }
+    }
+    if (g == 0 && j < D) p.o[(size_t)t * p.H * D + hd * D + j] = acc;
+  }
+#pragma unroll
+  for (int ii = 0; ii < DG; ++ii)
+    if (j < D && i_lo + ii < D) S_g[(size_t)(i_lo + ii) * D + j] = S[ii];
+  if (hd == 0) {
+    float* hp = p.h_prev + (size_t)rg.slot[s] * p.slot_stride;
+    for (int c = tid; c < p.width; c += blockDim.x) hp[c] = ld_f<T>((const T*)p.h + (size_t)(row_hi - 1) * p.width + c);
+  }
+}
+
 struct MlstmArgs {
   const float* q; const float* k; const float* v;  // [M, ld]; q/k head h at column h * D, v at h * V
   const float* ig; const float* fg;                // [M, ld] raw gate projections (bias not yet added), head h at column h
@@ -197,6 +260,86 @@ __global__ void mlstm_scan_kernel(const MlstmArgs p, const Ragged rg, const Scan
   __syncthreads();
   for (int e = tid; e < D * V; e += nt) S_g[e] = s_S[e];
   for (int e = tid; e < D; e += nt) n_g[e] = s_n[e];
+  if (tid == 0) *m_g = m;
+}
+
+// Register-resident variant of the mLSTM scan (see wkv_scan_reg_kernel): {q, k} travel as one float2 per state row.
+template <typename T, int DG>
+__global__ void __launch_bounds__(512) mlstm_scan_reg_kernel(const MlstmArgs p, const Ragged rg, const ScanShape sh) {
+  SSDK_DYN_SMEM(float2, sm2);
+  const int s = blockIdx.x, hd = blockIdx.y, D = p.D, V = p.V, tid = threadIdx.x;
+  const int j = tid % sh.Vr, g = tid / sh.Vr, i_lo = g * DG, rows = sh.G * DG;
+  float2* s_op = sm2;                                      // [rows] {q, k}
+  float* s_n = reinterpret_cast<float*>(s_op + rows);      // [rows]
+  float* s_part = s_n + rows;                              // [G][Vr]
+  float* s_dot = s_part + sh.G * sh.Vr;                    // [G]
+  const int row_lo = rg.cu[s], row_hi = rg.cu[s + 1];
+  if (row_hi <= row_lo) return;
+  const size_t slot = (size_t)rg.slot[s] * p.slot_stride;
+  float* S_g = p.S + slot + (size_t)hd * D * V;
+  float* n_g = p.n + slot + (size_t)hd * D;
+  float* m_g = p.m + slot + hd;
+  const bool fresh = rg.pos0[s] == 0;
+  float S[DG];
+#pragma unroll
+  for (int ii = 0; ii < DG; ++ii) S[ii] = (!fresh && j < V && i_lo + ii < D) ? S_g[(size_t)(i_lo + ii) * V + j] : 0.f;
+  if (tid < rows) s_n[tid] = (!fresh && tid < D) ? n_g[tid] : 0.f;
+  float m = fresh ? 0.f : *m_g;
+  const float ib = ld_f<T>((const T*)p.ib + hd), fb = ld_f<T>((const T*)p.fb + hd);
+  float nq = 0.f, nk = 0.f, nv = 0.f, ni, nf;
+  {
+    const size_t base = (size_t)row_lo * p.ld;
+    if (tid < D) { nq = p.q[base + hd * D + tid]; nk = p.k[base + hd * D + tid]; }
+    if (j < V) nv = p.v[base + hd * V + j];
+    ni = p.ig[base + hd]; nf = p.fg[base + hd];
+  }
+  for (int t = row_lo; t < row_hi; ++t) {
+    const float ig = p.cap * tanhf((ni + ib) / p.cap);
+    const float fg = log_sigmoid_f(p.cap * tanhf((nf + fb) / p.cap));
+    const float mn = fmaxf(fg + m, ig);
+    const float a = expf(fg + m - mn), b = expf(ig - mn);
+    m = mn;
+    __syncthreads();
+    if (tid < rows) {
+      s_op[tid] = tid < D ? make_float2(nq * p.q_scale, nk) : make_float2(0.f, 0.f);
+      s_n[tid] = fmaf(a, s_n[tid], b * (tid < D ? nk : 0.f));
+    }
+    const float bv = b * nv;
+    __syncthreads();
+    if (t + 1 < row_hi) {
+      const size_t nb = (size_t)(t + 1) * p.ld;
+      if (tid < D) { nq = p.q[nb + hd * D + tid]; nk = p.k[nb + hd * D + tid]; }
+      if (j < V) nv = p.v[nb + hd * V + j];
+      ni = p.ig[nb + hd]; nf = p.fg[nb + hd];
+    }
+    float acc = 0.f;
+#pragma unroll
+    for (int ii = 0; ii < DG; ++ii) {
+      const float2 o = s_op[i_lo + ii];
+      S[ii] = fmaf(a, S[ii], o.y * bv);
+      acc = fmaf(S[ii], o.x, acc);
+    }
+    if (j == 0) {
+      float dot = 0.f;
+#pragma unroll
+      for (int ii = 0; ii < DG; ++ii) dot = fmaf(s_n[i_lo + ii], s_op[i_lo + ii].x, dot);
+      s_dot[g] = dot;
+    }
+    s_part[g * sh.Vr + j] = acc;
+    __syncthreads();
+    if (g == 0 && j < V) {
+      acc = s_part[j];
+      float dot = s_dot[0];
+      for (int q = 1; q < sh.G; ++q) { acc += s_part[q * sh.Vr + j]; dot += s_dot[q]; }
+      const float den = fmaxf(fabsf(dot), expf(-m)) + 1e-6f;
+      p.o[(size_t)t * p.H * V + hd * V + j] = acc / den;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int ii = 0; ii < DG; ++ii)
+    if (j < V && i_lo + ii < D) S_g[(size_t)(i_lo + ii) * V + j] = S[ii];
+  if (tid < D) n_g[tid] = s_n[tid];
   if (tid == 0) *m_g = m;
 }
 
