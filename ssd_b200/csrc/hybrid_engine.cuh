@@ -160,10 +160,10 @@ static int64_t hyb_carve(ssdk_hyb_engine* e, uint8_t* base) {
   e->temps = (float*)take(lr * 4);
   e->meta_ints = 2 * cap + 3 * (size_t)g.max_seqs + 1 + (size_t)g.max_seqs * g.max_blocks_per_seq + lr;
   e->meta = (int*)take(e->meta_ints * 4);
-  // split-K partials of the tcgen05 GEMM at <= 64 rows: up to 8 splits of the widest output, bounded at 32 MB
+  // split-K partials of the tcgen05 GEMM: up to 8 splits of a 256-row call of the widest output, bounded at 64 MB
   size_t widest = std::max<size_t>(g.vocab, g.width);
   for (int w : {e->w_p0, e->w_p1, e->w_sff2}) widest = std::max<size_t>(widest, (size_t)w);
-  e->partial_floats = es == 2 ? std::min<size_t>(8 * 64 * widest, 8u << 20) : 0;
+  e->partial_floats = es == 2 ? std::min<size_t>(8 * std::min<size_t>(cap, 256) * widest, 16u << 20) : 0;
   e->partials = (float*)take(e->partial_floats * 4);
   return (int64_t)off;
 }
@@ -199,7 +199,8 @@ struct HybRun {
       const int m = std::min(kMaxTokens, m_total - r0), un = umma_n_for(m);
       const CUtensorMap* tmX;
       CKI(e->tmap((const bf16*)A + (size_t)r0 * K, m, K, un, &tmX));
-      int S = m <= 64 ? auto_splits(tiles, num_kb, 2) : 1;
+      // narrow outputs (a head projection is 8 .. 32 tiles) fill the machine by splitting K, at every row count
+      int S = auto_splits(tiles, num_kb, un <= 64 ? 2 : 1);
       while (S > 1 && (size_t)S * m * N > e->partial_floats) --S;
       GemmParams p;
       p.M = m; p.N = N; p.ldo = N; p.num_kb = num_kb; p.tile_rows = kTileRows; p.hi_row_offset = 64;

@@ -36,6 +36,7 @@ struct WkvArgs {
 struct ScanShape {
   int Vr, G, Dg;
 };
+constexpr int kScanPF = 4;  // rows of operands in flight in the register-resident scans
 
 template <typename T>
 __global__ void wkv_scan_kernel(const WkvArgs p, const Ragged rg, const ScanShape sh) {
@@ -127,39 +128,50 @@ __global__ void __launch_bounds__(512) wkv_scan_reg_kernel(const WkvArgs p, cons
   for (int ii = 0; ii < DG; ++ii) S[ii] = (!fresh && j < D && i_lo + ii < D) ? S_g[(size_t)(i_lo + ii) * D + j] : 0.f;
   float my_u = 0.f, my_w0 = 0.f;
   if (tid < D) { my_u = ld_f<T>((const T*)p.u + hd * D + tid); my_w0 = ld_f<T>((const T*)p.w0 + hd * D + tid); }
-  float nr = 0.f, nk = 0.f, nz = 0.f, nv = 0.f;
-  {
-    const size_t base = (size_t)row_lo * p.ld + hd * D;
-    if (tid < D) { nr = p.r[base + tid]; nk = p.k[base + tid]; nz = p.zw[base + tid]; }
-    if (j < D) nv = p.v[base + j];
-  }
-  for (int t = row_lo; t < row_hi; ++t) {
-    __syncthreads();
-    if (tid < rows) s_op[tid] = tid < D ? make_float4(nr, nk, expf(-expf(nz + my_w0)), my_u) : make_float4(0.f, 0.f, 0.f, 0.f);
-    const float vj = nv;
-    __syncthreads();
-    if (t + 1 < row_hi) {
-      const size_t nb = (size_t)(t + 1) * p.ld + hd * D;
-      if (tid < D) { nr = p.r[nb + tid]; nk = p.k[nb + tid]; nz = p.zw[nb + tid]; }
-      if (j < D) nv = p.v[nb + j];
-    }
-    float acc = 0.f;
+  // the operands of the next kScanPF rows are in flight (registers) while a row is computed: a row's arithmetic is far
+  // shorter than a trip to L2
+  float nr[kScanPF], nk[kScanPF], nz[kScanPF], nv[kScanPF];
 #pragma unroll
-    for (int ii = 0; ii < DG; ++ii) {
-      const float4 o = s_op[i_lo + ii];
-      const float kv = o.y * vj;
-      acc = fmaf(o.x, fmaf(o.w, kv, S[ii]), acc);
-      S[ii] = fmaf(o.z, S[ii], kv);
+  for (int u = 0; u < kScanPF; ++u) {
+    nr[u] = nk[u] = nz[u] = nv[u] = 0.f;
+    if (row_lo + u < row_hi) {
+      const size_t base = (size_t)(row_lo + u) * p.ld + hd * D;
+      if (tid < D) { nr[u] = p.r[base + tid]; nk[u] = p.k[base + tid]; nz[u] = p.zw[base + tid]; }
+      if (j < D) nv[u] = p.v[base + j];
     }
-    if (sh.G > 1) {
-      s_part[g * sh.Vr + j] = acc;
+  }
+  for (int t0 = row_lo; t0 < row_hi; t0 += kScanPF) {
+#pragma unroll
+    for (int u = 0; u < kScanPF; ++u) {
+      const int t = t0 + u;
+      if (t >= row_hi) break;
       __syncthreads();
-      if (g == 0) {
-        acc = s_part[j];
-        for (int q = 1; q < sh.G; ++q) acc += s_part[q * sh.Vr + j];
+      if (tid < rows) s_op[tid] = tid < D ? make_float4(nr[u], nk[u], expf(-expf(nz[u] + my_w0)), my_u) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float vj = nv[u];
+      __syncthreads();
+      if (t + kScanPF < row_hi) {
+        const size_t nb = (size_t)(t + kScanPF) * p.ld + hd * D;
+        if (tid < D) { nr[u] = p.r[nb + tid]; nk[u] = p.k[nb + tid]; nz[u] = p.zw[nb + tid]; }
+        if (j < D) nv[u] = p.v[nb + j];
       }
+      float acc = 0.f;
+#pragma unroll
+      for (int ii = 0; ii < DG; ++ii) {
+        const float4 o = s_op[i_lo + ii];
+        const float kv = o.y * vj;
+        acc = fmaf(o.x, fmaf(o.w, kv, S[ii]), acc);
+        S[ii] = fmaf(o.z, S[ii], kv);
+      }
+      if (sh.G > 1) {
+        s_part[g * sh.Vr + j] = acc;
+        __syncthreads();
+        if (g == 0) {
+          acc = s_part[j];
+          for (int q = 1; q < sh.G; ++q) acc += s_part[q * sh.Vr + j];
+        }
+      }
+      if (g == 0 && j < D) p.o[(size_t)t * p.H * D + hd * D + j] = acc;
     }
-    if (g == 0 && j < D) p.o[(size_t)t * p.H * D + hd * D + j] = acc;
   }
 #pragma unroll
   for (int ii = 0; ii < DG; ++ii)
@@ -286,53 +298,62 @@ __global__ void __launch_bounds__(512) mlstm_scan_reg_kernel(const MlstmArgs p, 
   if (tid < rows) s_n[tid] = (!fresh && tid < D) ? n_g[tid] : 0.f;
   float m = fresh ? 0.f : *m_g;
   const float ib = ld_f<T>((const T*)p.ib + hd), fb = ld_f<T>((const T*)p.fb + hd);
-  float nq = 0.f, nk = 0.f, nv = 0.f, ni, nf;
-  {
-    const size_t base = (size_t)row_lo * p.ld;
-    if (tid < D) { nq = p.q[base + hd * D + tid]; nk = p.k[base + hd * D + tid]; }
-    if (j < V) nv = p.v[base + hd * V + j];
-    ni = p.ig[base + hd]; nf = p.fg[base + hd];
+  float nq[kScanPF], nk[kScanPF], nv[kScanPF], ni[kScanPF], nf[kScanPF];
+#pragma unroll
+  for (int u = 0; u < kScanPF; ++u) {
+    nq[u] = nk[u] = nv[u] = ni[u] = nf[u] = 0.f;
+    if (row_lo + u < row_hi) {
+      const size_t base = (size_t)(row_lo + u) * p.ld;
+      if (tid < D) { nq[u] = p.q[base + hd * D + tid]; nk[u] = p.k[base + hd * D + tid]; }
+      if (j < V) nv[u] = p.v[base + hd * V + j];
+      ni[u] = p.ig[base + hd]; nf[u] = p.fg[base + hd];
+    }
   }
-  for (int t = row_lo; t < row_hi; ++t) {
-    const float ig = p.cap * tanhf((ni + ib) / p.cap);
-    const float fg = log_sigmoid_f(p.cap * tanhf((nf + fb) / p.cap));
-    const float mn = fmaxf(fg + m, ig);
-    const float a = expf(fg + m - mn), b = expf(ig - mn);
-    m = mn;
-    __syncthreads();
-    if (tid < rows) {
-      s_op[tid] = tid < D ? make_float2(nq * p.q_scale, nk) : make_float2(0.f, 0.f);
-      s_n[tid] = fmaf(a, s_n[tid], b * (tid < D ? nk : 0.f));
-    }
-    const float bv = b * nv;
-    __syncthreads();
-    if (t + 1 < row_hi) {
-      const size_t nb = (size_t)(t + 1) * p.ld;
-      if (tid < D) { nq = p.q[nb + hd * D + tid]; nk = p.k[nb + hd * D + tid]; }
-      if (j < V) nv = p.v[nb + hd * V + j];
-      ni = p.ig[nb + hd]; nf = p.fg[nb + hd];
-    }
-    float acc = 0.f;
+  for (int t0 = row_lo; t0 < row_hi; t0 += kScanPF) {
 #pragma unroll
-    for (int ii = 0; ii < DG; ++ii) {
-      const float2 o = s_op[i_lo + ii];
-      S[ii] = fmaf(a, S[ii], o.y * bv);
-      acc = fmaf(S[ii], o.x, acc);
-    }
-    if (j == 0) {
-      float dot = 0.f;
+    for (int u = 0; u < kScanPF; ++u) {
+      const int t = t0 + u;
+      if (t >= row_hi) break;
+      const float ig = p.cap * tanhf((ni[u] + ib) / p.cap);
+      const float fg = log_sigmoid_f(p.cap * tanhf((nf[u] + fb) / p.cap));
+      const float mn = fmaxf(fg + m, ig);
+      const float a = expf(fg + m - mn), b = expf(ig - mn);
+      m = mn;
+      __syncthreads();
+      if (tid < rows) {
+        s_op[tid] = tid < D ? make_float2(nq[u] * p.q_scale, nk[u]) : make_float2(0.f, 0.f);
+        s_n[tid] = fmaf(a, s_n[tid], b * (tid < D ? nk[u] : 0.f));
+      }
+      const float bv = b * nv[u];
+      __syncthreads();
+      if (t + kScanPF < row_hi) {
+        const size_t nb = (size_t)(t + kScanPF) * p.ld;
+        if (tid < D) { nq[u] = p.q[nb + hd * D + tid]; nk[u] = p.k[nb + hd * D + tid]; }
+        if (j < V) nv[u] = p.v[nb + hd * V + j];
+        ni[u] = p.ig[nb + hd]; nf[u] = p.fg[nb + hd];
+      }
+      float acc = 0.f;
 #pragma unroll
-      for (int ii = 0; ii < DG; ++ii) dot = fmaf(s_n[i_lo + ii], s_op[i_lo + ii].x, dot);
-      s_dot[g] = dot;
-    }
-    s_part[g * sh.Vr + j] = acc;
-    __syncthreads();
-    if (g == 0 && j < V) {
-      acc = s_part[j];
-      float dot = s_dot[0];
-      for (int q = 1; q < sh.G; ++q) { acc += s_part[q * sh.Vr + j]; dot += s_dot[q]; }
-      const float den = fmaxf(fabsf(dot), expf(-m)) + 1e-6f;
-      p.o[(size_t)t * p.H * V + hd * V + j] = acc / den;
+      for (int ii = 0; ii < DG; ++ii) {
+        const float2 o = s_op[i_lo + ii];
+        S[ii] = fmaf(a, S[ii], o.y * bv);
+        acc = fmaf(S[ii], o.x, acc);
+      }
+      if (j == 0) {
+        float dot = 0.f;
+#pragma unroll
+        for (int ii = 0; ii < DG; ++ii) dot = fmaf(s_n[i_lo + ii], s_op[i_lo + ii].x, dot);
+        s_dot[g] = dot;
+      }
+      s_part[g * sh.Vr + j] = acc;
+      __syncthreads();
+      if (g == 0 && j < V) {
+        acc = s_part[j];
+        float dot = s_dot[0];
+        for (int q = 1; q < sh.G; ++q) { acc += s_part[q * sh.Vr + j]; dot += s_dot[q]; }
+        const float den = fmaxf(fabsf(dot), expf(-m)) + 1e-6f;
+        p.o[(size_t)t * p.H * V + hd * V + j] = acc / den;
+      }
     }
   }
   __syncthreads();

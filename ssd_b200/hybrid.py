@@ -258,7 +258,8 @@ class HybridRunner:
         self.max_blocks = -(-max_model_len // block_size)
         self.max_model_len = max_model_len
         self.dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype]
-        self.max_logit_rows = max_logit_rows or max(1, min(max_tokens, (1 << 27) // spec.vocab))
+        # logits of one call live on the device as fp32 + bf16: all rows of a call unless that exceeds ~6 GB
+        self.max_logit_rows = max_logit_rows or max(1, min(max_tokens, (1 << 30) // spec.vocab))
         cfg = L.HybCfg(spec.width, spec.vocab, len(spec.layers), L.DT_BF16 if self.dtype == torch.bfloat16 else L.DT_F32,
                        spec.eps, max_tokens, max_seqs, self.max_logit_rows, block_size, self.max_blocks, 0)
         layer_cfgs = (L.HybLayerCfg * len(spec.layers))(*[l.cfg() for l in spec.layers])
@@ -298,7 +299,7 @@ class HybridRunner:
         `tokens` whose logits (and, with `temps`, sampled tokens) are asked for.  Returns (logits [n_want, vocab] float32
         or None, tokens list or None[, residual [layers, rows, width]]), rows in the order of the entries."""
         total = sum(len(e[0]) for e in entries)
-        if total > self.max_tokens or len(entries) > self.max_seqs:
+        if total > self.max_tokens or len(entries) > self.max_seqs or sum(len(e[4]) for e in entries) > self.max_logit_rows:
             return self._forward_split(entries, want_logits, temps, seed, residual)
         ids, cu, pos0, slots, want_rows = [], [0], [], [], []
         tables = np.full((len(entries), self.max_blocks), -1, dtype=np.int32)
@@ -335,19 +336,25 @@ class HybridRunner:
         cut, which the carried state and cache make equivalent to one call."""
         if residual:
             raise ValueError("the residual tap covers single calls only")
-        calls, cur, room = [], [], self.max_tokens
+        calls, cur, room, lroom = [], [], self.max_tokens, self.max_logit_rows
         first = np.cumsum([0] + [len(e[4]) for e in entries])  # first output row of every entry
         for i, (toks, p0, slot, table, want) in enumerate(entries):
+            if list(want) != sorted(want):
+                raise ValueError("wanted places must ascend")
             lo = 0
             while lo < len(toks):
-                if room == 0 or len(cur) == self.max_seqs:
+                if room == 0 or lroom == 0 or len(cur) == self.max_seqs:
                     calls.append(cur)
-                    cur, room = [], self.max_tokens
+                    cur, room, lroom = [], self.max_tokens, self.max_logit_rows
                 n = min(room, len(toks) - lo)
                 js = [j for j, k in enumerate(want) if lo <= k < lo + n]
+                if len(js) > lroom:  # cut the piece after the last wanted place that still fits this call
+                    js = js[:lroom]
+                    n = want[js[-1]] - lo + 1
                 cur.append(([first[i] + j for j in js], (toks[lo:lo + n], p0 + lo, slot, table, [want[j] - lo for j in js])))
                 lo += n
                 room -= n
+                lroom -= len(js)
         calls.append(cur)
         n_out = int(first[-1])
         logits = np.empty((n_out, self.spec.vocab), dtype=np.float32) if (want_logits and n_out) else None
