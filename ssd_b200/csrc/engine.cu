@@ -168,19 +168,21 @@ static int auto_splits(int tiles, int num_kb, int ctas_per_sm = 2) {
 
 template <int UN, int EPI>
 static int launch_gemm_inst(Launcher& L, const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int tiles,
-                            int splits) {
+                            int splits, int row_chunks) {
   using Cfg = GemmCfg<UN>;
   static bool attr_set = false;
   if (!attr_set) {
     CK(cudaFuncSetAttribute(gemm_ws_kernel<UN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     attr_set = true;
   }
-  return L.go(gemm_ws_kernel<UN, EPI>, dim3(tiles, splits), dim3(kGemmThreads), (size_t)Cfg::kSmemBytes, tmW, tmX, p);
+  if (row_chunks > 1 && EPI != EPI_PARTIAL) return fail("row chunks are an EPI_PARTIAL feature");
+  return L.go(gemm_ws_kernel<UN, EPI>, dim3(tiles, splits, row_chunks), dim3(kGemmThreads), (size_t)Cfg::kSmemBytes, tmW, tmX, p);
 }
+// row_chunks > 1 (EPI_PARTIAL): p.M rows in chunks of umma_n along gridDim.z, tmX covering all of them
 static int launch_gemm(Launcher& L, int umma_n, int epi, const CUtensorMap& tmW, const CUtensorMap& tmX,
-                       const GemmParams& p, int tiles, int splits) {
+                       const GemmParams& p, int tiles, int splits, int row_chunks = 1) {
 #define SSDK_GEMM_CASE(UN, EP) \
-  if (umma_n == UN && epi == EP) return launch_gemm_inst<UN, EP>(L, tmW, tmX, p, tiles, splits);
+  if (umma_n == UN && epi == EP) return launch_gemm_inst<UN, EP>(L, tmW, tmX, p, tiles, splits, row_chunks);
   SSDK_GEMM_CASE(16, EPI_BF16) SSDK_GEMM_CASE(16, EPI_PARTIAL) SSDK_GEMM_CASE(16, EPI_SILU) SSDK_GEMM_CASE(16, EPI_PUBLISH)
   SSDK_GEMM_CASE(32, EPI_BF16) SSDK_GEMM_CASE(32, EPI_PARTIAL) SSDK_GEMM_CASE(32, EPI_SILU) SSDK_GEMM_CASE(32, EPI_PUBLISH)
   SSDK_GEMM_CASE(64, EPI_BF16) SSDK_GEMM_CASE(64, EPI_PARTIAL) SSDK_GEMM_CASE(64, EPI_SILU) SSDK_GEMM_CASE(64, EPI_PUBLISH)

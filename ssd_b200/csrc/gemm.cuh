@@ -52,7 +52,7 @@ struct PublishParams {
 
 struct GemmParams {
   void* out;          // EPI_BF16/EPI_SILU: bf16 [M, ldo]; EPI_PARTIAL: fp32 [S, M, N]
-  int M;              // valid tokens (<= UMMA_N)
+  int M;              // valid tokens: <= UMMA_N, or (EPI_PARTIAL only) any count when gridDim.z = ceil(M / UMMA_N) row chunks
   int N;              // output width (weight rows; for EPI_SILU the ffn width)
   int ldo;            // output row stride in elements
   int num_kb;         // total k-blocks (K / 64)
@@ -145,6 +145,9 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   const int nkb = min(p.kb_per_split, p.num_kb - kb0);
   const int row_lo = (EPI == EPI_SILU) ? tile * 64 : tile * kTileRows;
   const int row_hi = row_lo + p.hi_row_offset;
+  // row chunk (prefill-sized EPI_PARTIAL calls): this CTA multiplies tokens m_base .. m_base + m_valid of the X map
+  const int m_base = (int)blockIdx.z * UMMA_N;
+  const int m_valid = min(UMMA_N, p.M - m_base);
 
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmW);
@@ -185,7 +188,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       trace_mark(TR_GEMM);
       for (int i = 0; i < pre; ++i) {
         uint8_t* b_s = smem + i * Cfg::kStageBytes + Cfg::kABytes;
-        tma_load_2d(b_s, &tmX, &full_bar[i], (kb0 + i) * kBlockK, 0, kEvictLast);
+        tma_load_2d(b_s, &tmX, &full_bar[i], (kb0 + i) * kBlockK, m_base, kEvictLast);
       }
       for (int i = pre; i < nkb; ++i) {
         const int s = i % kStages;
@@ -196,7 +199,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         const int k = (kb0 + i) * kBlockK;
         tma_load_2d(a_s, &tmW, &full_bar[s], k, row_lo, kEvictFirst);
         tma_load_2d(a_s + Cfg::kABytes / 2, &tmW, &full_bar[s], k, row_hi, kEvictFirst);
-        tma_load_2d(a_s + Cfg::kABytes, &tmX, &full_bar[s], k, 0, kEvictLast);
+        tma_load_2d(a_s + Cfg::kABytes, &tmX, &full_bar[s], k, m_base, kEvictLast);
       }
     }
   } else if (warp == 1) {
@@ -230,7 +233,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     if (threadIdx.x == 64) trace_fine(TRF_GEMM + 0);  // CTA 0's accumulator complete
     constexpr int CW = Cfg::kEpiCols;
     // the accumulator is drained in passes of CW token columns (one pass for UMMA_N <= 64); token index = m0 + m
-    for (int m0 = 0; m0 < UMMA_N && m0 < p.M; m0 += CW) {
+    for (int m0 = 0; m0 < UMMA_N && m0 < m_valid; m0 += CW) {
     uint32_t r[CW];
 #pragma unroll
     for (int c = 0; c < CW / 16; ++c) tmem_ld_32x32b_x16(tmem_d + ((uint32_t)(q * 32) << 16) + m0 + c * 16, r + c * 16);
@@ -247,10 +250,10 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     } else if (EPI == EPI_PARTIAL) {
       const int n = row_lo + row;
       if (n < p.N) {
-        float* out = reinterpret_cast<float*>(p.out) + (size_t)blockIdx.y * p.M * p.N;
+        float* out = reinterpret_cast<float*>(p.out) + ((size_t)blockIdx.y * p.M + m_base) * p.N;
 #pragma unroll
         for (int m = 0; m < CW; ++m)
-          if (m0 + m < p.M) out[(size_t)(m0 + m) * p.N + n] = __uint_as_float(r[m]);
+          if (m0 + m < m_valid) out[(size_t)(m0 + m) * p.N + n] = __uint_as_float(r[m]);
       }
     } else if (EPI == EPI_PUBLISH) {
       const PublishParams& pb = p.pub;

@@ -192,28 +192,25 @@ struct HybRun {
            ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0;
   }
   int lin_tc(const void* A, const void* W, float* C, int m_total, int N, int K) {
-    const CUtensorMap* tmW;
+    const CUtensorMap *tmW, *tmX;
     CKI(e->tmap(W, N, K, 64, &tmW));
+    // one launch for all rows: chunks of `un` tokens along gridDim.z share the weight tiles through L2
+    const int un = umma_n_for(std::min(m_total, kMaxTokens)), chunks = (m_total + un - 1) / un;
+    CKI(e->tmap(A, m_total, K, un, &tmX));
     const int tiles = (N + kTileRows - 1) / kTileRows, num_kb = K / kBlockK;
-    for (int r0 = 0; r0 < m_total; r0 += kMaxTokens) {
-      const int m = std::min(kMaxTokens, m_total - r0), un = umma_n_for(m);
-      const CUtensorMap* tmX;
-      CKI(e->tmap((const bf16*)A + (size_t)r0 * K, m, K, un, &tmX));
-      // narrow outputs (a head projection is 8 .. 32 tiles) fill the machine by splitting K, at every row count
-      int S = auto_splits(tiles, num_kb, un <= 64 ? 2 : 1);
-      while (S > 1 && (size_t)S * m * N > e->partial_floats) --S;
-      GemmParams p;
-      p.M = m; p.N = N; p.ldo = N; p.num_kb = num_kb; p.tile_rows = kTileRows; p.hi_row_offset = 64;
-      p.sk_partials = nullptr; p.sk_counters = nullptr; p.sk_width = 0;
-      p.kb_per_split = (num_kb + S - 1) / S;
-      S = (num_kb + p.kb_per_split - 1) / p.kb_per_split;
-      float* dst = C + (size_t)r0 * N;
-      p.out = S == 1 ? dst : e->partials;
-      CKI(launch_gemm(L, un, EPI_PARTIAL, *tmW, *tmX, p, tiles, S));
-      if (S > 1) {
-        const size_t n = (size_t)m * N;
-        CKI(L.go(ssdk::splitk_sum_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (const float*)e->partials, dst, S, n));
-      }
+    // narrow outputs (a head projection is 8 .. 32 tiles) with few row chunks fill the machine by splitting K
+    int S = auto_splits(tiles * chunks, num_kb, un <= 64 ? 2 : 1);
+    while (S > 1 && (size_t)S * m_total * N > e->partial_floats) --S;
+    GemmParams p;
+    p.M = m_total; p.N = N; p.ldo = N; p.num_kb = num_kb; p.tile_rows = kTileRows; p.hi_row_offset = 64;
+    p.sk_partials = nullptr; p.sk_counters = nullptr; p.sk_width = 0;
+    p.kb_per_split = (num_kb + S - 1) / S;
+    S = (num_kb + p.kb_per_split - 1) / p.kb_per_split;
+    p.out = S == 1 ? C : e->partials;
+    CKI(launch_gemm(L, un, EPI_PARTIAL, *tmW, *tmX, p, tiles, S, chunks));
+    if (S > 1) {
+      const size_t n = (size_t)m_total * N;
+      CKI(L.go(ssdk::splitk_sum_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (const float*)e->partials, C, S, n));
     }
     return 0;
   }

@@ -234,6 +234,27 @@ def test_bfloat16_storage(tmp_path, width):
     assert np.abs(np.concatenate(out) - whole).max() < 1e-4 * np.abs(whole).max()
 
 
+def test_bfloat16_calls_of_many_rows(tmp_path):
+    """More rows than one tile of the tcgen05 GEMM holds (256): the dense projections run as row chunks of one launch, the
+    last chunk partly filled; two prompts of unequal length in one call, against the oracle and against portions that
+    each fit a single tile."""
+    every = dict(experts=4, top=4, groups=2, keep=2, ff=64, shared_ff=64)
+    cfg = U.config([U.wkv(heads=2, dim=32, rank=64, mlp=U.moe(**every)), U.latent(heads=2, dim=32, rot_dim=16, vdim=32, kv_rank=64, q_rank=64),
+                    U.mlstm(heads=2, dim=32, vdim=64, mlp=U.moe(**every))], width=128, vocab=96)
+    r, plain, _ = _runner(tmp_path, cfg, dtype="bfloat16", max_tokens=1024, max_model_len=512, num_blocks=64)
+    seqs = [_tokens(330, cfg["vocab"], 80), _tokens(271, cfg["vocab"], 81)]
+    refs = [plain.run(s).numpy() for s in seqs]
+    lg, _ = r.forward([(s, 0, i, _pages(len(s), 16, 30 * i), list(range(len(s)))) for i, s in enumerate(seqs)])
+    got = [lg[:330], lg[330:]]
+    for g, ref in zip(got, refs):
+        assert U.rel_err(g, ref) < BF16_TOL
+    out, pos = [], 0
+    for c in [200, 100, 30]:
+        out.append(r.forward([(seqs[0][pos:pos + c], pos, 2, _pages(330, 16, 30), list(range(c)))])[0])
+        pos += c
+    assert U.rel_err(np.concatenate(out), got[0]) < 2e-2
+
+
 def test_greedy_generation_through_llm(tmp_path):
     """The public entry point: LLM.generate with the engine's scheduler (three prompts, two state slots: the third
     waits for a slot and gets a used one), temperature 0, against the oracle's greedy continuation."""
