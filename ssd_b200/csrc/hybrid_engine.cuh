@@ -50,6 +50,7 @@ struct ssdk_hyb_engine {
   int* h_meta = nullptr;     // pinned staging of the step's integers
   // tcgen05 path of the dense bf16 products: TMA descriptors by (pointer, rows, K, box rows), split-K partials
   bool use_tc = true;
+  bool use_decode_attn = true;  // fused single-token latent attention (SSDK_HYB_DECODE_ATTN=0: GEMM path for every row)
   std::map<std::tuple<const void*, int64_t, int, int>, CUtensorMap> tmaps;
   float* partials = nullptr; size_t partial_floats = 0;
   int tmap(const void* ptr, int64_t rows, int K, int box_rows, const CUtensorMap** out) {
@@ -359,8 +360,31 @@ struct HybRun {
              H, D, R, KR, c.rot_dims));
     // absorption: qcat[m, h, :kv_rank] = W_uk,h^T qn[m, h, :]
     CKI(lin(e->t1, H * D, Lr.t[SSDK_HT_LAT_UKT].p, D, e->qcat, H * Wd, M, KR, D, true, H, D, (long long)KR * D, Wd));
+    // single-token sequences (decode) share ONE fused launch + a merge; the others take the GEMM path below
+    bool fused_decode = false;
+    {
+      int n_dec = 0, ctx_max = 0;
+      for (int s = 0; s < rg.n_seqs; ++s)
+        if (h_cu[s + 1] - h_cu[s] == 1) { ++n_dec; ctx_max = std::max(ctx_max, h_pos0[s] + 1); }
+      const size_t smem = ssdk::latent_decode_smem(H, KR, Wd, sizeof(T));
+      if (n_dec > 0 && smem <= 200 * 1024 && e->use_decode_attn) {
+        // ~2 CTAs per SM over all sequences, at least 64 keys per split, partials within the score buffer
+        int splits = std::max(1, std::min({32, 2 * num_sms() / n_dec, (ctx_max + 63) / 64}));
+        const size_t per_split = (size_t)rg.n_seqs * H * (KR + 2);
+        splits = (int)std::min<size_t>(splits, e->att_elems / per_split);
+        if (splits >= 1) {
+          ssdk::LatentDecodeArgs da;
+          da.qcat = e->qcat; da.cache = pool; da.sink = Lr.t[SSDK_HT_LAT_SINK].p; da.part = e->att_s; da.out = e->t0;
+          da.H = H; da.KR = KR; da.W = Wd; da.splits = splits; da.scale = c.attn_scale;
+          CKI(L.go(ssdk::latent_decode_partial_kernel<T>, dim3(rg.n_seqs, splits), dim3(ssdk::kDecThreads), smem, da, rg));
+          CKI(L.go(ssdk::latent_decode_merge_kernel<T>, dim3(rg.n_seqs, H), dim3(128), 0, da, rg));
+          fused_decode = true;
+        }
+      }
+    }
     for (int s = 0; s < rg.n_seqs; ++s) {
       const int r0 = h_cu[s], n = h_cu[s + 1] - r0, p0 = h_pos0[s], ctx = p0 + n, ctx_pad = (ctx + 7) / 8 * 8;
+      if (fused_decode && n == 1) continue;
       CKI(L.go(ssdk::latent_gather_kernel<T>, dim3(ctx_pad), dim3(128), 0, (const T*)pool, (T*)e->keys, (T*)e->lat_t, rg, s, ctx, ctx_pad,
                KR, Wd));
       const int qb = (int)std::max<size_t>(1, e->att_elems / ((size_t)H * ctx_pad));
@@ -438,6 +462,8 @@ static int hyb_smem_attrs(ssdk_hyb_engine* e) {
   CK(cudaFuncSetAttribute(ssdk::wkv_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   CK(cudaFuncSetAttribute(ssdk::mlstm_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   CK(cudaFuncSetAttribute(ssdk::mlstm_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+  CK(cudaFuncSetAttribute(ssdk::latent_decode_partial_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+  CK(cudaFuncSetAttribute(ssdk::latent_decode_partial_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   e->smem_attr_done = true;
   return 0;
 }
@@ -516,6 +542,7 @@ int ssdk_hyb_create(const ssdk_hyb_cfg* cfg, const ssdk_hyb_layer_cfg* layers, s
   e->cfg = *cfg;
   e->esz = cfg->dtype == SSDK_DT_BF16 ? 2 : 4;
   e->use_tc = env_int("SSDK_HYB_TCGEN05", 1) != 0;
+  e->use_decode_attn = env_int("SSDK_HYB_DECODE_ATTN", 1) != 0;
   e->layers.resize(cfg->n_layers);
   for (int i = 0; i < cfg->n_layers; ++i) e->layers[i].c = layers[i];
   if (hyb_derive(e) != 0) { delete e; return -1; }

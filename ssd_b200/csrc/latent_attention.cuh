@@ -16,6 +16,9 @@
 //                        (token, head) pairs as rows (every head meets the same keys: multi-query), sink_softmax_kernel
 //                        (fp32: causal edge per row, the sink as one more term of the denominator with no key and no
 //                        value), output = P C.  Accumulation runs over keys in index order, whatever the portion.
+//   single-token rows    (decode) skip the gather and the GEMMs: latent_decode_partial_kernel walks the pages of ALL such
+//                        sequences in one launch, split along the context (scores, running maximum and P C per split,
+//                        fp32), latent_decode_merge_kernel joins the splits and adds the sink to the denominator.
 #pragma once
 #include "layer_ops.cuh"
 
@@ -131,6 +134,117 @@ __global__ void sink_softmax_kernel(const float* __restrict__ sc, T* __restrict_
   sum = block_sum(sum, red) + expf(sk - mx);
   const float inv = 1.0f / sum;
   for (int j = threadIdx.x; j < ld; j += blockDim.x) st_f<T>(pr + (size_t)r * ld + j, j < n ? expf(srow[j] * scale - mx) * inv : 0.f);
+}
+
+// ---- single-token (decode) rows: one launch over all such sequences, the context split flash-decoding style ----
+struct LatentDecodeArgs {
+  const void* qcat;   // [M, H, W] T: latent-space query | rotated part
+  const void* cache;  // [rows, W] T (this layer's pool)
+  const void* sink;   // [H] T
+  float* part;        // [n_seqs, splits, H, KR + 2] fp32: unnormalised P C | running maximum | running sum
+  void* out;          // [M, H, KR] T
+  int H, KR, W, splits;
+  float scale;
+};
+
+constexpr int kDecTile = 16, kDecThreads = 256;
+
+inline size_t latent_decode_smem(int H, int KR, int W, size_t esz) {
+  return ((size_t)H * W + (size_t)H * kDecTile + (size_t)H * KR + 3 * (size_t)H) * 4 + (size_t)kDecTile * W * esz + 16;
+}
+
+// grid (n_seqs, splits); a sequence that brings more than one row is left to the GEMM path
+template <typename T>
+__global__ void __launch_bounds__(kDecThreads) latent_decode_partial_kernel(const LatentDecodeArgs p, const Ragged rg) {
+  const int s = blockIdx.x, j = blockIdx.y;
+  const int row = rg.cu[s];
+  if (rg.cu[s + 1] - row != 1) return;
+  const int H = p.H, KR = p.KR, W = p.W;
+  extern __shared__ __align__(16) uint8_t dec_smem[];
+  float* qs = (float*)dec_smem;            // [H, W] query times scale
+  float* ps = qs + (size_t)H * W;          // [H, kDecTile] scores, then weights
+  float* acc = ps + (size_t)H * kDecTile;  // [H, KR]
+  float* mx = acc + (size_t)H * KR;        // [H] running maximum
+  float* ls = mx + H;                      // [H] running sum
+  float* rs = ls + H;                      // [H] rescale of this tile
+  T* ct = (T*)(rs + H);                    // [kDecTile, W] key rows
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int ctx = rg.pos0[s] + 1, per = (ctx + p.splits - 1) / p.splits;
+  const int k_lo = j * per, k_hi = min(ctx, k_lo + per);
+  const T* q = (const T*)p.qcat + (size_t)row * H * W;
+  for (int i = tid; i < H * W; i += kDecThreads) qs[i] = ld_f<T>(q + i) * p.scale;
+  for (int i = tid; i < H * KR; i += kDecThreads) acc[i] = 0.f;
+  for (int i = tid; i < H; i += kDecThreads) { mx[i] = -INFINITY; ls[i] = 0.f; }
+  __syncthreads();
+  for (int k0 = k_lo; k0 < k_hi; k0 += kDecTile) {
+    const int nk = min(kDecTile, k_hi - k0);
+    for (int k = warp; k < nk; k += kDecThreads / 32) {
+      const T* src = (const T*)p.cache + page_row(rg, s, k0 + k) * (size_t)W;
+      for (int d = lane; d < W; d += 32) ct[k * W + d] = src[d];
+    }
+    __syncthreads();
+    for (int pr = warp; pr < kDecTile * H; pr += kDecThreads / 32) {
+      const int k = pr % kDecTile, h = pr / kDecTile;
+      float a = 0.f;
+      if (k < nk)
+        for (int d = lane; d < W; d += 32) a = fmaf(qs[h * W + d], ld_f<T>(ct + k * W + d), a);
+      a = warp_sum(a);
+      if (lane == 0) ps[h * kDecTile + k] = k < nk ? a : -INFINITY;
+    }
+    __syncthreads();
+    for (int h = tid; h < H; h += kDecThreads) {
+      float m_new = mx[h];
+      for (int k = 0; k < nk; ++k) m_new = fmaxf(m_new, ps[h * kDecTile + k]);
+      const float r = mx[h] == -INFINITY ? 0.f : expf(mx[h] - m_new);
+      float sum = ls[h] * r;
+      for (int k = 0; k < kDecTile; ++k) {
+        const float w = k < nk ? expf(ps[h * kDecTile + k] - m_new) : 0.f;
+        ps[h * kDecTile + k] = w;
+        sum += w;
+      }
+      mx[h] = m_new; ls[h] = sum; rs[h] = r;
+    }
+    __syncthreads();
+    for (int o = tid; o < H * KR; o += kDecThreads) {
+      const int h = o / KR, c = o - h * KR;
+      float a = acc[o] * rs[h];
+      for (int k = 0; k < nk; ++k) a = fmaf(ps[h * kDecTile + k], ld_f<T>(ct + k * W + c), a);
+      acc[o] = a;
+    }
+    __syncthreads();
+  }
+  float* dst = p.part + ((size_t)s * p.splits + j) * H * (KR + 2);
+  for (int o = tid; o < H * KR; o += kDecThreads) dst[(size_t)(o / KR) * (KR + 2) + o % KR] = acc[o];
+  for (int h = tid; h < H; h += kDecThreads) { dst[(size_t)h * (KR + 2) + KR] = mx[h]; dst[(size_t)h * (KR + 2) + KR + 1] = ls[h]; }
+}
+
+// grid (n_seqs, H): out = sum_j e^(m_j - m) acc_j / (e^(sink - m) + sum_j e^(m_j - m) l_j), m = max(sink, max_j m_j)
+template <typename T>
+__global__ void latent_decode_merge_kernel(const LatentDecodeArgs p, const Ragged rg) {
+  const int s = blockIdx.x, h = blockIdx.y;
+  const int row = rg.cu[s];
+  if (rg.cu[s + 1] - row != 1) return;
+  const int KR = p.KR;
+  const float* part = p.part + ((size_t)s * p.splits * p.H + h) * (KR + 2);
+  const size_t js = (size_t)p.H * (KR + 2);  // floats between two splits of one head
+  const float sk = ld_f<T>((const T*)p.sink + h);
+  float m = sk;
+  for (int j = 0; j < p.splits; ++j) m = fmaxf(m, part[j * js + KR]);
+  float den = expf(sk - m);
+  for (int j = 0; j < p.splits; ++j) {
+    const float mj = part[j * js + KR];
+    if (mj != -INFINITY) den += expf(mj - m) * part[j * js + KR + 1];
+  }
+  const float inv = 1.0f / den;
+  T* out = (T*)p.out + ((size_t)row * p.H + h) * KR;
+  for (int c = threadIdx.x; c < KR; c += blockDim.x) {
+    float a = 0.f;
+    for (int j = 0; j < p.splits; ++j) {
+      const float mj = part[j * js + KR];
+      if (mj != -INFINITY) a = fmaf(expf(mj - m), part[j * js + c], a);
+    }
+    st_f<T>(out + c, a * inv);
+  }
 }
 
 }  // namespace ssdk

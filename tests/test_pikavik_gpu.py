@@ -231,7 +231,8 @@ def test_bfloat16_storage(tmp_path, width):
     for c in [2, 30, 3, 64, 2] + [1] * 19:
         out.append(r.forward([(toks[pos:pos + c], pos, 1, _pages(n, 16, 9), list(range(c)))])[0])
         pos += c
-    assert np.abs(np.concatenate(out) - whole).max() < 1e-4 * np.abs(whole).max()
+    # single-token rows take the fused decode attention, which keeps its weights in fp32: equal up to bf16 rounding
+    assert U.rel_err(np.concatenate(out), whole) < 1e-2
 
 
 def test_bfloat16_calls_of_many_rows(tmp_path):
