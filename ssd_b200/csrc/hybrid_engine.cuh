@@ -375,7 +375,7 @@ struct HybRun {
         if (splits >= 1) {
           ssdk::LatentDecodeArgs da;
           da.qcat = e->qcat; da.cache = pool; da.sink = Lr.t[SSDK_HT_LAT_SINK].p; da.part = e->att_s; da.out = e->t0;
-          da.H = H; da.KR = KR; da.W = Wd; da.splits = splits; da.scale = c.attn_scale;
+          da.H = H; da.KR = KR; da.W = Wd; da.splits = splits; da.scale = c.attn_scale; da.pool_aligned = ((uintptr_t)pool & 15) == 0;
           CKI(L.go(ssdk::latent_decode_partial_kernel<T>, dim3(rg.n_seqs, splits), dim3(ssdk::kDecThreads), smem, da, rg));
           CKI(L.go(ssdk::latent_decode_merge_kernel<T>, dim3(rg.n_seqs, H), dim3(128), 0, da, rg));
           fused_decode = true;

@@ -144,6 +144,7 @@ struct LatentDecodeArgs {
   float* part;        // [n_seqs, splits, H, KR + 2] fp32: unnormalised P C | running maximum | running sum
   void* out;          // [M, H, KR] T
   int H, KR, W, splits;
+  int pool_aligned;   // the pool starts on a 16-byte boundary
   float scale;
 };
 
@@ -172,15 +173,28 @@ __global__ void __launch_bounds__(kDecThreads) latent_decode_partial_kernel(cons
   const int ctx = rg.pos0[s] + 1, per = (ctx + p.splits - 1) / p.splits;
   const int k_lo = j * per, k_hi = min(ctx, k_lo + per);
   const T* q = (const T*)p.qcat + (size_t)row * H * W;
+  constexpr int kPerVec = 16 / (int)sizeof(T);
+  // rows of the pool start on 16-byte boundaries when W is a multiple of a vector (the pool itself is 16-byte aligned)
+  const bool vec = p.pool_aligned && W % kPerVec == 0 && ((size_t)(H * W + H * kDecTile + H * KR + 3 * H) * 4) % 16 == 0;
   for (int i = tid; i < H * W; i += kDecThreads) qs[i] = ld_f<T>(q + i) * p.scale;
   for (int i = tid; i < H * KR; i += kDecThreads) acc[i] = 0.f;
   for (int i = tid; i < H; i += kDecThreads) { mx[i] = -INFINITY; ls[i] = 0.f; }
   __syncthreads();
   for (int k0 = k_lo; k0 < k_hi; k0 += kDecTile) {
     const int nk = min(kDecTile, k_hi - k0);
-    for (int k = warp; k < nk; k += kDecThreads / 32) {
-      const T* src = (const T*)p.cache + page_row(rg, s, k0 + k) * (size_t)W;
-      for (int d = lane; d < W; d += 32) ct[k * W + d] = src[d];
+    if (vec) {  // 16-byte loads, every thread several in flight
+      const int vpr = W / kPerVec;
+#pragma unroll 4
+      for (int i = tid; i < nk * vpr; i += kDecThreads) {
+        const int k = i / vpr, v = i - k * vpr;
+        const uint4* src = (const uint4*)((const T*)p.cache + page_row(rg, s, k0 + k) * (size_t)W);
+        ((uint4*)ct)[i] = __ldg(src + v);
+      }
+    } else {
+      for (int k = warp; k < nk; k += kDecThreads / 32) {
+        const T* src = (const T*)p.cache + page_row(rg, s, k0 + k) * (size_t)W;
+        for (int d = lane; d < W; d += 32) ct[k * W + d] = src[d];
+      }
     }
     __syncthreads();
     for (int pr = warp; pr < kDecTile * H; pr += kDecThreads / 32) {
