@@ -169,6 +169,8 @@ static int64_t hyb_carve(ssdk_hyb_engine* e, uint8_t* base) {
   return (int64_t)off;
 }
 
+constexpr size_t kScanSmemMax = 200 * 1024;  // dynamic shared memory the scans may ask for
+
 template <typename T>
 struct HybRun {
   ssdk_hyb_engine* e;
@@ -288,8 +290,9 @@ struct HybRun {
     a.o = e->p2; a.state = st; a.slot_stride = e->slot_floats; a.h = e->h; a.h_prev = h_prev; a.width = W; a.H = H; a.D = D;
     int dg = 0;
     ssdk::ScanShape sh = reg_scan_shape(D, D, &dg);
-    if (dg) {
-      const size_t smem = (size_t)sh.G * dg * 16 + (size_t)sh.G * sh.Vr * 4;
+    const size_t reg_smem = dg ? ssdk::wkv_scan_reg_smem(D, sh, dg) : 0;
+    if (dg && reg_smem <= kScanSmemMax) {
+      const size_t smem = reg_smem;
       const dim3 grid(rg.n_seqs, H), block(sh.Vr * sh.G);
       if (dg == 8) CKI(L.go(ssdk::wkv_scan_reg_kernel<T, 8>, grid, block, smem, a, rg, sh));
       else if (dg == 16) CKI(L.go(ssdk::wkv_scan_reg_kernel<T, 16>, grid, block, smem, a, rg, sh));
@@ -322,8 +325,9 @@ struct HybRun {
     a.H = H; a.D = D; a.V = V; a.cap = c.gate_cap; a.q_scale = 1.0f / sqrtf((float)D);
     int dg = 0;
     ssdk::ScanShape sh = reg_scan_shape(D, V, &dg);
-    if (dg) {
-      const size_t smem = (size_t)sh.G * dg * 12 + (size_t)(sh.G * sh.Vr + sh.G) * 4;
+    const size_t reg_smem = dg ? ssdk::mlstm_scan_reg_smem(D, V, sh, dg) : 0;
+    if (dg && reg_smem <= kScanSmemMax) {
+      const size_t smem = reg_smem;
       const dim3 grid(rg.n_seqs, H), block(sh.Vr * sh.G);
       if (dg == 8) CKI(L.go(ssdk::mlstm_scan_reg_kernel<T, 8>, grid, block, smem, a, rg, sh));
       else if (dg == 16) CKI(L.go(ssdk::mlstm_scan_reg_kernel<T, 16>, grid, block, smem, a, rg, sh));
@@ -462,6 +466,13 @@ static int hyb_smem_attrs(ssdk_hyb_engine* e) {
   CK(cudaFuncSetAttribute(ssdk::wkv_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   CK(cudaFuncSetAttribute(ssdk::mlstm_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   CK(cudaFuncSetAttribute(ssdk::mlstm_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+#define SSDK_SCAN_ATTR(DG) \
+  CK(cudaFuncSetAttribute(ssdk::wkv_scan_reg_kernel<bf16, DG>, cudaFuncAttributeMaxDynamicSharedMemorySize, big)); \
+  CK(cudaFuncSetAttribute(ssdk::wkv_scan_reg_kernel<float, DG>, cudaFuncAttributeMaxDynamicSharedMemorySize, big)); \
+  CK(cudaFuncSetAttribute(ssdk::mlstm_scan_reg_kernel<bf16, DG>, cudaFuncAttributeMaxDynamicSharedMemorySize, big)); \
+  CK(cudaFuncSetAttribute(ssdk::mlstm_scan_reg_kernel<float, DG>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+  SSDK_SCAN_ATTR(8) SSDK_SCAN_ATTR(16) SSDK_SCAN_ATTR(32)
+#undef SSDK_SCAN_ATTR
   CK(cudaFuncSetAttribute(ssdk::latent_decode_partial_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   CK(cudaFuncSetAttribute(ssdk::latent_decode_partial_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   e->smem_attr_done = true;

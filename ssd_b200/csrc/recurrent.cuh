@@ -36,7 +36,6 @@ struct WkvArgs {
 struct ScanShape {
   int Vr, G, Dg;
 };
-constexpr int kScanPF = 4;  // rows of operands in flight in the register-resident scans
 
 template <typename T>
 __global__ void wkv_scan_kernel(const WkvArgs p, const Ragged rg, const ScanShape sh) {
@@ -109,16 +108,35 @@ __global__ void wkv_scan_kernel(const WkvArgs p, const Ragged rg, const ScanShap
 }
 
 // Register-resident variant: every thread keeps its DG rows of its column in registers for the whole portion (the state
-// never touches shared memory), the per-row operands {r, k, w, u} travel as ONE float4 per state row (rows beyond the
-// head size are zero operands), so a state row costs one broadcast shared-memory load instead of six accesses.
-// Launched when G * DG >= D with DG in {8, 16, 32} fits a CTA; the shared-memory kernel above serves every other size.
+// never touches shared memory).  Rows are taken in chunks of kScanChunk: the chunk's raw operands arrive by cp.async while
+// the previous chunk is computed, all threads turn them into one float4 {r, k, w = exp(-exp(z + w0)), u} per (row, state
+// row) at once, and then every thread walks the chunk with nothing but broadcast shared-memory loads and FMAs; the G
+// partial read-outs of a column are summed (fixed order g = 0 .. G-1) for the whole chunk afterwards.  Four CTA barriers
+// per chunk instead of three per row.  Launched when G * DG >= D with DG in {8, 16, 32} fits a CTA and its shared
+// memory; the shared-memory kernel above serves every other size.
+constexpr int kScanChunk = 16;
+
+SSDK_DEVINL void cp_async4(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+
+inline size_t wkv_scan_reg_smem(int D, const ScanShape& sh, int DG) {
+  const size_t C = kScanChunk, rows = (size_t)sh.G * DG;
+  return C * rows * 16 + (C * sh.Vr + C * sh.G * sh.Vr + 4 * C * D + 2 * rows) * 4;
+}
+
 template <typename T, int DG>
 __global__ void __launch_bounds__(512) wkv_scan_reg_kernel(const WkvArgs p, const Ragged rg, const ScanShape sh) {
   SSDK_DYN_SMEM(float4, sm4);
-  const int s = blockIdx.x, hd = blockIdx.y, D = p.D, tid = threadIdx.x;
-  const int j = tid % sh.Vr, g = tid / sh.Vr, i_lo = g * DG, rows = sh.G * DG;
-  float4* s_op = sm4;                                        // [rows] {r, k, w, u}
-  float* s_part = reinterpret_cast<float*>(s_op + rows);     // [G][Vr]
+  constexpr int C = kScanChunk;
+  const int s = blockIdx.x, hd = blockIdx.y, D = p.D, tid = threadIdx.x, nt = blockDim.x;
+  const int Vr = sh.Vr, G = sh.G, j = tid % Vr, g = tid / Vr, i_lo = g * DG, rows = G * DG;
+  float4* s_op = sm4;                                          // [C][rows] {r, k, w, u}
+  float* s_v = reinterpret_cast<float*>(s_op + C * rows);      // [C][Vr]
+  float* s_part = s_v + C * Vr;                                // [C][G][Vr]
+  float* raw = s_part + C * G * Vr;                            // r | k | z | v, each [C][D], as the projections left them
+  float* s_w0 = raw + 4 * C * D;                               // [rows]
+  float* s_u = s_w0 + rows;                                    // [rows]
   const int row_lo = rg.cu[s], row_hi = rg.cu[s + 1];
   if (row_hi <= row_lo) return;
   float* S_g = p.state + (size_t)rg.slot[s] * p.slot_stride + (size_t)hd * D * D;
@@ -126,51 +144,61 @@ __global__ void __launch_bounds__(512) wkv_scan_reg_kernel(const WkvArgs p, cons
   float S[DG];
 #pragma unroll
   for (int ii = 0; ii < DG; ++ii) S[ii] = (!fresh && j < D && i_lo + ii < D) ? S_g[(size_t)(i_lo + ii) * D + j] : 0.f;
-  float my_u = 0.f, my_w0 = 0.f;
-  if (tid < D) { my_u = ld_f<T>((const T*)p.u + hd * D + tid); my_w0 = ld_f<T>((const T*)p.w0 + hd * D + tid); }
-  // the operands of the next kScanPF rows are in flight (registers) while a row is computed: a row's arithmetic is far
-  // shorter than a trip to L2
-  float nr[kScanPF], nk[kScanPF], nz[kScanPF], nv[kScanPF];
-#pragma unroll
-  for (int u = 0; u < kScanPF; ++u) {
-    nr[u] = nk[u] = nz[u] = nv[u] = 0.f;
-    if (row_lo + u < row_hi) {
-      const size_t base = (size_t)(row_lo + u) * p.ld + hd * D;
-      if (tid < D) { nr[u] = p.r[base + tid]; nk[u] = p.k[base + tid]; nz[u] = p.zw[base + tid]; }
-      if (j < D) nv[u] = p.v[base + j];
-    }
+  for (int i = tid; i < rows; i += nt) {
+    s_w0[i] = i < D ? ld_f<T>((const T*)p.w0 + hd * D + i) : 0.f;
+    s_u[i] = i < D ? ld_f<T>((const T*)p.u + hd * D + i) : 0.f;
   }
-  for (int t0 = row_lo; t0 < row_hi; t0 += kScanPF) {
-#pragma unroll
-    for (int u = 0; u < kScanPF; ++u) {
-      const int t = t0 + u;
-      if (t >= row_hi) break;
-      __syncthreads();
-      if (tid < rows) s_op[tid] = tid < D ? make_float4(nr[u], nk[u], expf(-expf(nz[u] + my_w0)), my_u) : make_float4(0.f, 0.f, 0.f, 0.f);
-      const float vj = nv[u];
-      __syncthreads();
-      if (t + kScanPF < row_hi) {
-        const size_t nb = (size_t)(t + kScanPF) * p.ld + hd * D;
-        if (tid < D) { nr[u] = p.r[nb + tid]; nk[u] = p.k[nb + tid]; nz[u] = p.zw[nb + tid]; }
-        if (j < D) nv[u] = p.v[nb + j];
-      }
+  auto issue = [&](int t0) {
+    const int n = min(C, row_hi - t0);
+    for (int e = tid; e < n * D; e += nt) {
+      const int c = e / D, i = e - c * D;
+      const size_t src = (size_t)(t0 + c) * p.ld + hd * D + i;
+      cp_async4(raw + e, p.r + src);
+      cp_async4(raw + C * D + e, p.k + src);
+      cp_async4(raw + 2 * C * D + e, p.zw + src);
+      cp_async4(raw + 3 * C * D + e, p.v + src);
+    }
+    cp_async_commit();
+  };
+  issue(row_lo);
+  for (int t0 = row_lo; t0 < row_hi; t0 += C) {
+    const int n = min(C, row_hi - t0);
+    cp_async_wait<0>();
+    __syncthreads();  // the chunk's operands have landed; the previous chunk's readers of s_op / s_v / s_part are done
+    for (int e = tid; e < n * rows; e += nt) {
+      const int c = e / rows, i = e - c * rows;
+      s_op[e] = i < D ? make_float4(raw[c * D + i], raw[C * D + c * D + i], expf(-expf(raw[2 * C * D + c * D + i] + s_w0[i])), s_u[i])
+                      : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int e = tid; e < n * Vr; e += nt) {
+      const int c = e / Vr, jj = e - c * Vr;
+      s_v[e] = jj < D ? raw[3 * C * D + c * D + jj] : 0.f;
+    }
+    __syncthreads();
+    if (t0 + C < row_hi) issue(t0 + C);
+    for (int c = 0; c < n; ++c) {
+      const float vj = s_v[c * Vr + j];
+      const float4* op = s_op + c * rows + i_lo;
       float acc = 0.f;
 #pragma unroll
       for (int ii = 0; ii < DG; ++ii) {
-        const float4 o = s_op[i_lo + ii];
+        const float4 o = op[ii];
         const float kv = o.y * vj;
         acc = fmaf(o.x, fmaf(o.w, kv, S[ii]), acc);
         S[ii] = fmaf(o.z, S[ii], kv);
       }
-      if (sh.G > 1) {
-        s_part[g * sh.Vr + j] = acc;
-        __syncthreads();
-        if (g == 0) {
-          acc = s_part[j];
-          for (int q = 1; q < sh.G; ++q) acc += s_part[q * sh.Vr + j];
-        }
+      if (G > 1) s_part[(c * G + g) * Vr + j] = acc;
+      else if (j < D) p.o[(size_t)(t0 + c) * p.H * D + hd * D + j] = acc;
+    }
+    if (G > 1) {
+      __syncthreads();
+      for (int e = tid; e < n * Vr; e += nt) {
+        const int c = e / Vr, jj = e - c * Vr;
+        if (jj >= D) continue;
+        float acc = s_part[(c * G) * Vr + jj];
+        for (int q = 1; q < G; ++q) acc += s_part[(c * G + q) * Vr + jj];
+        p.o[(size_t)(t0 + c) * p.H * D + hd * D + jj] = acc;
       }
-      if (g == 0 && j < D) p.o[(size_t)t * p.H * D + hd * D + j] = acc;
     }
   }
 #pragma unroll
@@ -275,16 +303,33 @@ __global__ void mlstm_scan_kernel(const MlstmArgs p, const Ragged rg, const Scan
   if (tid == 0) *m_g = m;
 }
 
-// Register-resident variant of the mLSTM scan (see wkv_scan_reg_kernel): {q, k} travel as one float2 per state row.
+// Register-resident, chunked variant of the mLSTM scan (see wkv_scan_reg_kernel): {q, k} travel as one float2 per (row,
+// state row).  The gates of a chunk are evaluated by warp 0 — capped gates in parallel, the stabiliser's max-chain row
+// by row with exactly the sequential arithmetic, then the two exponentials in parallel.  The normaliser n lives in the
+// registers of each row group's first thread, which updates it beside its state column.
+inline size_t mlstm_scan_reg_smem(int D, int V, const ScanShape& sh, int DG) {
+  const size_t C = kScanChunk, rows = (size_t)sh.G * DG;
+  return C * rows * 8 + (C * sh.Vr + C * sh.G * sh.Vr + C * sh.G + 3 * C + 2 * C * D + C * V + 2 * C) * 4 + 16;
+}
+
 template <typename T, int DG>
 __global__ void __launch_bounds__(512) mlstm_scan_reg_kernel(const MlstmArgs p, const Ragged rg, const ScanShape sh) {
   SSDK_DYN_SMEM(float2, sm2);
-  const int s = blockIdx.x, hd = blockIdx.y, D = p.D, V = p.V, tid = threadIdx.x;
-  const int j = tid % sh.Vr, g = tid / sh.Vr, i_lo = g * DG, rows = sh.G * DG;
-  float2* s_op = sm2;                                      // [rows] {q, k}
-  float* s_n = reinterpret_cast<float*>(s_op + rows);      // [rows]
-  float* s_part = s_n + rows;                              // [G][Vr]
-  float* s_dot = s_part + sh.G * sh.Vr;                    // [G]
+  constexpr int C = kScanChunk;
+  const int s = blockIdx.x, hd = blockIdx.y, D = p.D, V = p.V, tid = threadIdx.x, nt = blockDim.x;
+  const int Vr = sh.Vr, G = sh.G, j = tid % Vr, g = tid / Vr, i_lo = g * DG, rows = G * DG;
+  float2* s_op = sm2;                                      // [C][rows] {q * scale, k}
+  float* s_v = reinterpret_cast<float*>(s_op + C * rows);  // [C][Vr]
+  float* s_part = s_v + C * Vr;                            // [C][G][Vr]
+  float* s_dot = s_part + C * G * Vr;                      // [C][G]
+  float* s_a = s_dot + C * G;                              // [C] decay of the row
+  float* s_b = s_a + C;                                    // [C] input weight of the row
+  float* s_m = s_b + C;                                    // [C] stabiliser after the row
+  float* raw_q = s_m + C;                                  // [C][D]
+  float* raw_k = raw_q + C * D;                            // [C][D]
+  float* raw_v = raw_k + C * D;                            // [C][V]
+  float* raw_i = raw_v + C * V;                            // [C]
+  float* raw_f = raw_i + C;                                // [C]
   const int row_lo = rg.cu[s], row_hi = rg.cu[s + 1];
   if (row_hi <= row_lo) return;
   const size_t slot = (size_t)rg.slot[s] * p.slot_stride;
@@ -292,75 +337,106 @@ __global__ void __launch_bounds__(512) mlstm_scan_reg_kernel(const MlstmArgs p, 
   float* n_g = p.n + slot + (size_t)hd * D;
   float* m_g = p.m + slot + hd;
   const bool fresh = rg.pos0[s] == 0;
-  float S[DG];
+  float S[DG], nn[DG];
 #pragma unroll
-  for (int ii = 0; ii < DG; ++ii) S[ii] = (!fresh && j < V && i_lo + ii < D) ? S_g[(size_t)(i_lo + ii) * V + j] : 0.f;
-  if (tid < rows) s_n[tid] = (!fresh && tid < D) ? n_g[tid] : 0.f;
-  float m = fresh ? 0.f : *m_g;
-  const float ib = ld_f<T>((const T*)p.ib + hd), fb = ld_f<T>((const T*)p.fb + hd);
-  float nq[kScanPF], nk[kScanPF], nv[kScanPF], ni[kScanPF], nf[kScanPF];
-#pragma unroll
-  for (int u = 0; u < kScanPF; ++u) {
-    nq[u] = nk[u] = nv[u] = ni[u] = nf[u] = 0.f;
-    if (row_lo + u < row_hi) {
-      const size_t base = (size_t)(row_lo + u) * p.ld;
-      if (tid < D) { nq[u] = p.q[base + hd * D + tid]; nk[u] = p.k[base + hd * D + tid]; }
-      if (j < V) nv[u] = p.v[base + hd * V + j];
-      ni[u] = p.ig[base + hd]; nf[u] = p.fg[base + hd];
-    }
+  for (int ii = 0; ii < DG; ++ii) {
+    S[ii] = (!fresh && j < V && i_lo + ii < D) ? S_g[(size_t)(i_lo + ii) * V + j] : 0.f;
+    nn[ii] = (!fresh && j == 0 && i_lo + ii < D) ? n_g[i_lo + ii] : 0.f;
   }
-  for (int t0 = row_lo; t0 < row_hi; t0 += kScanPF) {
-#pragma unroll
-    for (int u = 0; u < kScanPF; ++u) {
-      const int t = t0 + u;
-      if (t >= row_hi) break;
-      const float ig = p.cap * tanhf((ni[u] + ib) / p.cap);
-      const float fg = log_sigmoid_f(p.cap * tanhf((nf[u] + fb) / p.cap));
-      const float mn = fmaxf(fg + m, ig);
-      const float a = expf(fg + m - mn), b = expf(ig - mn);
-      m = mn;
-      __syncthreads();
-      if (tid < rows) {
-        s_op[tid] = tid < D ? make_float2(nq[u] * p.q_scale, nk[u]) : make_float2(0.f, 0.f);
-        s_n[tid] = fmaf(a, s_n[tid], b * (tid < D ? nk[u] : 0.f));
+  float m = fresh ? 0.f : *m_g;  // tracked by warp 0
+  const float ib = ld_f<T>((const T*)p.ib + hd), fb = ld_f<T>((const T*)p.fb + hd);
+  auto issue = [&](int t0) {
+    const int n = min(C, row_hi - t0);
+    for (int e = tid; e < n * D; e += nt) {
+      const int c = e / D, i = e - c * D;
+      const size_t src = (size_t)(t0 + c) * p.ld + hd * D + i;
+      cp_async4(raw_q + e, p.q + src);
+      cp_async4(raw_k + e, p.k + src);
+    }
+    for (int e = tid; e < n * V; e += nt) {
+      const int c = e / V, jj = e - c * V;
+      cp_async4(raw_v + e, p.v + (size_t)(t0 + c) * p.ld + hd * V + jj);
+    }
+    if (tid < n) {
+      cp_async4(raw_i + tid, p.ig + (size_t)(t0 + tid) * p.ld + hd);
+      cp_async4(raw_f + tid, p.fg + (size_t)(t0 + tid) * p.ld + hd);
+    }
+    cp_async_commit();
+  };
+  issue(row_lo);
+  for (int t0 = row_lo; t0 < row_hi; t0 += C) {
+    const int n = min(C, row_hi - t0);
+    cp_async_wait<0>();
+    __syncthreads();
+    for (int e = tid; e < n * rows; e += nt) {
+      const int c = e / rows, i = e - c * rows;
+      s_op[e] = i < D ? make_float2(raw_q[c * D + i] * p.q_scale, raw_k[c * D + i]) : make_float2(0.f, 0.f);
+    }
+    for (int e = tid; e < n * Vr; e += nt) {
+      const int c = e / Vr, jj = e - c * Vr;
+      s_v[e] = jj < V ? raw_v[c * V + jj] : 0.f;
+    }
+    if (tid < 32) {
+      static_assert(C <= 32, "a chunk's gates are one warp's lanes");
+      const int c = tid;
+      float ig = 0.f, fg = 0.f;
+      if (c < n) {
+        ig = p.cap * tanhf((raw_i[c] + ib) / p.cap);
+        fg = log_sigmoid_f(p.cap * tanhf((raw_f[c] + fb) / p.cap));
       }
-      const float bv = b * nv[u];
-      __syncthreads();
-      if (t + kScanPF < row_hi) {
-        const size_t nb = (size_t)(t + kScanPF) * p.ld;
-        if (tid < D) { nq[u] = p.q[nb + hd * D + tid]; nk[u] = p.k[nb + hd * D + tid]; }
-        if (j < V) nv[u] = p.v[nb + hd * V + j];
-        ni[u] = p.ig[nb + hd]; nf[u] = p.fg[nb + hd];
+      float m_prev = 0.f, m_new = 0.f;
+      for (int cc = 0; cc < n; ++cc) {
+        const float ic = __shfl_sync(0xffffffffu, ig, cc), fc = __shfl_sync(0xffffffffu, fg, cc);
+        const float mn = fmaxf(fc + m, ic);
+        if (c == cc) { m_prev = m; m_new = mn; }
+        m = mn;
       }
+      if (c < n) {
+        s_a[c] = expf(fg + m_prev - m_new);
+        s_b[c] = expf(ig - m_new);
+        s_m[c] = m_new;
+      }
+    }
+    __syncthreads();
+    if (t0 + C < row_hi) issue(t0 + C);
+    for (int c = 0; c < n; ++c) {
+      const float a = s_a[c], b = s_b[c];
+      const float bv = b * s_v[c * Vr + j];
+      const float2* op = s_op + c * rows + i_lo;
       float acc = 0.f;
 #pragma unroll
       for (int ii = 0; ii < DG; ++ii) {
-        const float2 o = s_op[i_lo + ii];
+        const float2 o = op[ii];
         S[ii] = fmaf(a, S[ii], o.y * bv);
         acc = fmaf(S[ii], o.x, acc);
       }
       if (j == 0) {
         float dot = 0.f;
 #pragma unroll
-        for (int ii = 0; ii < DG; ++ii) dot = fmaf(s_n[i_lo + ii], s_op[i_lo + ii].x, dot);
-        s_dot[g] = dot;
+        for (int ii = 0; ii < DG; ++ii) {
+          const float2 o = op[ii];
+          nn[ii] = fmaf(a, nn[ii], b * o.y);
+          dot = fmaf(nn[ii], o.x, dot);
+        }
+        s_dot[c * G + g] = dot;
       }
-      s_part[g * sh.Vr + j] = acc;
-      __syncthreads();
-      if (g == 0 && j < V) {
-        acc = s_part[j];
-        float dot = s_dot[0];
-        for (int q = 1; q < sh.G; ++q) { acc += s_part[q * sh.Vr + j]; dot += s_dot[q]; }
-        const float den = fmaxf(fabsf(dot), expf(-m)) + 1e-6f;
-        p.o[(size_t)t * p.H * V + hd * V + j] = acc / den;
-      }
+      s_part[(c * G + g) * Vr + j] = acc;
+    }
+    __syncthreads();
+    for (int e = tid; e < n * Vr; e += nt) {
+      const int c = e / Vr, jj = e - c * Vr;
+      if (jj >= V) continue;
+      float acc = s_part[(c * G) * Vr + jj], dot = s_dot[c * G];
+      for (int q = 1; q < G; ++q) { acc += s_part[(c * G + q) * Vr + jj]; dot += s_dot[c * G + q]; }
+      const float den = fmaxf(fabsf(dot), expf(-s_m[c])) + 1e-6f;
+      p.o[(size_t)(t0 + c) * p.H * V + hd * V + jj] = acc / den;
     }
   }
-  __syncthreads();
 #pragma unroll
-  for (int ii = 0; ii < DG; ++ii)
+  for (int ii = 0; ii < DG; ++ii) {
     if (j < V && i_lo + ii < D) S_g[(size_t)(i_lo + ii) * V + j] = S[ii];
-  if (tid < D) n_g[tid] = s_n[tid];
+    if (j == 0 && i_lo + ii < D) n_g[i_lo + ii] = nn[ii];
+  }
   if (tid == 0) *m_g = m;
 }
 
