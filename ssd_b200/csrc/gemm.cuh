@@ -249,17 +249,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       }
     } else if (EPI == EPI_PARTIAL) {
       const int n = row_lo + row;
-      if (p.sk_counters != nullptr) {
-        // in-kernel split-K reduction (single-pass shapes: UMMA_N <= 64, one row chunk): the last CTA of a tile sums the
-        // partials in the fixed order s = 0..S-1 and stores the fp32 result; no separate reduction launch
-        if (!splitk_ticket_reduce<CW>(r, p, n < p.N ? n : -1, tile, &pub_last)) goto epilogue_done;
-        if (n < p.N) {
-          float* out = reinterpret_cast<float*>(p.out);
-#pragma unroll
-          for (int m = 0; m < CW; ++m)
-            if (m0 + m < m_valid) out[(size_t)(m0 + m) * p.N + n] = __uint_as_float(r[m]);
-        }
-      } else if (n < p.N) {
+      if (n < p.N) {
         float* out = reinterpret_cast<float*>(p.out) + ((size_t)blockIdx.y * p.M + m_base) * p.N;
 #pragma unroll
         for (int m = 0; m < CW; ++m)

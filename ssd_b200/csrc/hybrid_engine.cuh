@@ -53,7 +53,6 @@ struct ssdk_hyb_engine {
   bool use_decode_attn = true;  // fused single-token latent attention (SSDK_HYB_DECODE_ATTN=0: GEMM path for every row)
   std::map<std::tuple<const void*, int64_t, int, int>, CUtensorMap> tmaps;
   float* partials = nullptr; size_t partial_floats = 0;
-  unsigned* sk_counters = nullptr;
   int tmap(const void* ptr, int64_t rows, int K, int box_rows, const CUtensorMap** out) {
     auto key = std::make_tuple(ptr, rows, K, box_rows);
     auto it = tmaps.find(key);
@@ -116,8 +115,6 @@ static int hyb_derive(ssdk_hyb_engine* e) {
   return 0;
 }
 
-constexpr int kSkCounters = 1024;  // output tiles a ticket-reduced split-K launch may have
-
 // workspace carve: base == nullptr only sizes it
 static int64_t hyb_carve(ssdk_hyb_engine* e, uint8_t* base) {
   const ssdk_hyb_cfg& g = e->cfg;
@@ -169,7 +166,6 @@ static int64_t hyb_carve(ssdk_hyb_engine* e, uint8_t* base) {
   for (int w : {e->w_p0, e->w_p1, e->w_sff2}) widest = std::max<size_t>(widest, (size_t)w);
   e->partial_floats = es == 2 ? std::min<size_t>(8 * std::min<size_t>(cap, 256) * widest, 16u << 20) : 0;
   e->partials = (float*)take(e->partial_floats * 4);
-  e->sk_counters = (unsigned*)take(kSkCounters * 4);  // split-K arrival tickets: zero at bind time, zero again after every launch
   return (int64_t)off;
 }
 
@@ -213,12 +209,9 @@ struct HybRun {
     p.sk_partials = nullptr; p.sk_counters = nullptr; p.sk_width = 0;
     p.kb_per_split = (num_kb + S - 1) / S;
     S = (num_kb + p.kb_per_split - 1) / p.kb_per_split;
-    // few rows (decode): the last CTA of a tile reduces the splits itself; prefill-sized calls use the separate sum
-    const bool ticket = S > 1 && un <= 64 && chunks == 1 && tiles <= kSkCounters && e->sk_counters != nullptr;
-    if (ticket) { p.sk_partials = e->partials; p.sk_counters = e->sk_counters; p.sk_width = N; }
-    p.out = (S == 1 || ticket) ? C : e->partials;
+    p.out = S == 1 ? C : e->partials;
     CKI(launch_gemm(L, un, EPI_PARTIAL, *tmW, *tmX, p, tiles, S, chunks));
-    if (S > 1 && !ticket) {
+    if (S > 1) {
       const size_t n = (size_t)m_total * N;
       CKI(L.go(ssdk::splitk_sum_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (const float*)e->partials, C, S, n));
     }
@@ -625,7 +618,6 @@ int ssdk_hyb_bind_pools(ssdk_hyb_handle e, void* cache, int64_t num_blocks, void
   if (((uintptr_t)workspace & 255) || ((uintptr_t)cache & 15) || ((uintptr_t)state & 15)) return fail("ssdk_hyb_bind_pools: misaligned pool");
   e->cache = (uint8_t*)cache; e->num_blocks = num_blocks; e->state = (float*)state; e->n_slots = n_slots;
   hyb_carve(e, (uint8_t*)workspace);
-  CK(cudaMemset(e->sk_counters, 0, kSkCounters * 4));
   return 0;
 }
 
