@@ -151,20 +151,29 @@ struct LatentDecodeArgs {
 constexpr int kDecTile = 16, kDecThreads = 256;
 
 inline size_t latent_decode_smem(int H, int KR, int W, size_t esz) {
-  return ((size_t)H * W + (size_t)H * kDecTile + (size_t)H * KR + 3 * (size_t)H) * 4 + (size_t)kDecTile * W * esz + 16;
+  const size_t Hp = (size_t)(H + 3) / 4 * 4;
+  return (kDecTile * Hp + (size_t)H * W + (size_t)H * KR + 3 * (size_t)H) * 4 + (size_t)kDecTile * W * esz + 16;
 }
 
-// grid (n_seqs, splits); a sequence that brings more than one row is left to the GEMM path
+template <typename T> SSDK_DEVINL float2 ld_pair(const T* p);
+template <> SSDK_DEVINL float2 ld_pair<float>(const float* p) { return make_float2(p[0], p[1]); }
+template <> SSDK_DEVINL float2 ld_pair<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+
+// grid (n_seqs, splits); a sequence that brings more than one row is left to the GEMM path.  Both products are
+// register-blocked over heads so that one shared-memory load feeds several FMAs: a warp scores one key against four
+// heads at a time (two dimensions per lane and step), a thread accumulates one latent column for eight heads at a time.
 template <typename T>
 __global__ void __launch_bounds__(kDecThreads) latent_decode_partial_kernel(const LatentDecodeArgs p, const Ragged rg) {
   const int s = blockIdx.x, j = blockIdx.y;
   const int row = rg.cu[s];
   if (rg.cu[s + 1] - row != 1) return;
-  const int H = p.H, KR = p.KR, W = p.W;
+  const int H = p.H, KR = p.KR, W = p.W, Hp = (H + 3) / 4 * 4;
   extern __shared__ __align__(16) uint8_t dec_smem[];
-  float* qs = (float*)dec_smem;            // [H, W] query times scale
-  float* ps = qs + (size_t)H * W;          // [H, kDecTile] scores, then weights
-  float* acc = ps + (size_t)H * kDecTile;  // [H, KR]
+  float* ps = (float*)dec_smem;            // [kDecTile, Hp] scores, then weights (columns H .. Hp stay zero)
+  float* qs = ps + kDecTile * Hp;          // [H, W] query times scale
+  float* acc = qs + (size_t)H * W;         // [H, KR]
   float* mx = acc + (size_t)H * KR;        // [H] running maximum
   float* ls = mx + H;                      // [H] running sum
   float* rs = ls + H;                      // [H] rescale of this tile
@@ -174,12 +183,16 @@ __global__ void __launch_bounds__(kDecThreads) latent_decode_partial_kernel(cons
   const int k_lo = j * per, k_hi = min(ctx, k_lo + per);
   const T* q = (const T*)p.qcat + (size_t)row * H * W;
   constexpr int kPerVec = 16 / (int)sizeof(T);
+  const size_t ct_off = ((size_t)kDecTile * Hp + (size_t)H * W + (size_t)H * KR + 3 * (size_t)H) * 4;
   // rows of the pool start on 16-byte boundaries when W is a multiple of a vector (the pool itself is 16-byte aligned)
-  const bool vec = p.pool_aligned && W % kPerVec == 0 && ((size_t)(H * W + H * kDecTile + H * KR + 3 * H) * 4) % 16 == 0;
+  const bool vec = p.pool_aligned && W % kPerVec == 0 && ct_off % 16 == 0;
+  const bool pairs = W % 2 == 0;  // (the key tile starts on a 4-byte boundary, which a bf16 pair needs)
   for (int i = tid; i < H * W; i += kDecThreads) qs[i] = ld_f<T>(q + i) * p.scale;
   for (int i = tid; i < H * KR; i += kDecThreads) acc[i] = 0.f;
+  for (int i = tid; i < kDecTile * Hp; i += kDecThreads) ps[i] = 0.f;
   for (int i = tid; i < H; i += kDecThreads) { mx[i] = -INFINITY; ls[i] = 0.f; }
   __syncthreads();
+  const int hq = Hp / 4;
   for (int k0 = k_lo; k0 < k_hi; k0 += kDecTile) {
     const int nk = min(kDecTile, k_hi - k0);
     if (vec) {  // 16-byte loads, every thread several in flight
@@ -197,33 +210,67 @@ __global__ void __launch_bounds__(kDecThreads) latent_decode_partial_kernel(cons
       }
     }
     __syncthreads();
-    for (int pr = warp; pr < kDecTile * H; pr += kDecThreads / 32) {
-      const int k = pr % kDecTile, h = pr / kDecTile;
-      float a = 0.f;
-      if (k < nk)
-        for (int d = lane; d < W; d += 32) a = fmaf(qs[h * W + d], ld_f<T>(ct + k * W + d), a);
-      a = warp_sum(a);
-      if (lane == 0) ps[h * kDecTile + k] = k < nk ? a : -INFINITY;
+    for (int pr = warp; pr < kDecTile * hq; pr += kDecThreads / 32) {
+      const int k = pr % kDecTile, h0 = (pr / kDecTile) * 4;
+      float a[4] = {0.f, 0.f, 0.f, 0.f};
+      if (k < nk) {
+        const T* kr = ct + k * W;
+        if (pairs) {
+          for (int d = 2 * lane; d < W; d += 64) {
+            const float2 x = ld_pair<T>(kr + d);
+#pragma unroll
+            for (int hh = 0; hh < 4; ++hh)
+              if (h0 + hh < H) {
+                const float2 qv = *reinterpret_cast<const float2*>(qs + (size_t)(h0 + hh) * W + d);
+                a[hh] = fmaf(qv.x, x.x, fmaf(qv.y, x.y, a[hh]));
+              }
+          }
+        } else {
+          for (int d = lane; d < W; d += 32) {
+            const float x = ld_f<T>(kr + d);
+#pragma unroll
+            for (int hh = 0; hh < 4; ++hh)
+              if (h0 + hh < H) a[hh] = fmaf(qs[(size_t)(h0 + hh) * W + d], x, a[hh]);
+          }
+        }
+      }
+#pragma unroll
+      for (int hh = 0; hh < 4; ++hh) {
+        const float v = warp_sum(a[hh]);
+        if (lane == 0 && h0 + hh < H) ps[k * Hp + h0 + hh] = k < nk ? v : -INFINITY;
+      }
     }
     __syncthreads();
     for (int h = tid; h < H; h += kDecThreads) {
       float m_new = mx[h];
-      for (int k = 0; k < nk; ++k) m_new = fmaxf(m_new, ps[h * kDecTile + k]);
+      for (int k = 0; k < nk; ++k) m_new = fmaxf(m_new, ps[k * Hp + h]);
       const float r = mx[h] == -INFINITY ? 0.f : expf(mx[h] - m_new);
       float sum = ls[h] * r;
       for (int k = 0; k < kDecTile; ++k) {
-        const float w = k < nk ? expf(ps[h * kDecTile + k] - m_new) : 0.f;
-        ps[h * kDecTile + k] = w;
+        const float w = k < nk ? expf(ps[k * Hp + h] - m_new) : 0.f;
+        ps[k * Hp + h] = w;
         sum += w;
       }
       mx[h] = m_new; ls[h] = sum; rs[h] = r;
     }
     __syncthreads();
-    for (int o = tid; o < H * KR; o += kDecThreads) {
-      const int h = o / KR, c = o - h * KR;
-      float a = acc[o] * rs[h];
-      for (int k = 0; k < nk; ++k) a = fmaf(ps[h * kDecTile + k], ld_f<T>(ct + k * W + c), a);
-      acc[o] = a;
+    for (int c = tid; c < KR; c += kDecThreads) {
+      for (int h0 = 0; h0 < H; h0 += 8) {
+        float a[8];
+#pragma unroll
+        for (int hh = 0; hh < 8; ++hh) a[hh] = h0 + hh < H ? acc[(size_t)(h0 + hh) * KR + c] * rs[h0 + hh] : 0.f;
+        const bool second = h0 + 4 < Hp;
+        for (int k = 0; k < nk; ++k) {
+          const float x = ld_f<T>(ct + k * W + c);
+          const float4 p0 = *reinterpret_cast<const float4*>(ps + k * Hp + h0);
+          const float4 p1 = second ? *reinterpret_cast<const float4*>(ps + k * Hp + h0 + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+          a[0] = fmaf(p0.x, x, a[0]); a[1] = fmaf(p0.y, x, a[1]); a[2] = fmaf(p0.z, x, a[2]); a[3] = fmaf(p0.w, x, a[3]);
+          a[4] = fmaf(p1.x, x, a[4]); a[5] = fmaf(p1.y, x, a[5]); a[6] = fmaf(p1.z, x, a[6]); a[7] = fmaf(p1.w, x, a[7]);
+        }
+#pragma unroll
+        for (int hh = 0; hh < 8; ++hh)
+          if (h0 + hh < H) acc[(size_t)(h0 + hh) * KR + c] = a[hh];
+      }
     }
     __syncthreads();
   }
