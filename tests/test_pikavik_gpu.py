@@ -185,6 +185,31 @@ def test_far_keys_page_borders_and_sink(tmp_path):
     assert U.rel_err(PlainModel(cfg, t0).run(toks[:40]).numpy(), ref[:40]) > 0.05
 
 
+def test_decoding_sequences_of_unequal_context_share_a_step(tmp_path):
+    """Three sequences decode together at contexts of a few, ~150 and ~300 tokens beside a prompt portion of a fourth: the
+    single-token rows take the split-context attention (some splits of the short sequence hold no key at all), the
+    portion the GEMM path, in one call.  Sharp scores (large scale) make a wrong or missing far key visible."""
+    cfg = U.config([U.latent(heads=3, dim=8, rot_dim=8, vdim=10, kv_rank=12, q_rank=12, scale=4.0, mlp=U.moe()),
+                    U.wkv(), U.latent(heads=5, dim=6, rot_dim=4, vdim=6, kv_rank=9, q_rank=8, scale=2.0)])
+    r, plain, _ = _runner(tmp_path, cfg, seed=5, max_tokens=512, max_model_len=512, num_blocks=64)
+    lens, steps = [3, 150, 300, 90], 6
+    seqs = [_tokens(n + steps, cfg["vocab"], 90 + i) for i, n in enumerate(lens)]
+    refs = [plain.run(s).numpy() for s in seqs]
+    pages = [_pages(len(s), 16, first) for s, first in zip(seqs, (58, 40, 5, 30))]
+    for i in range(3):  # prompts of the decoding sequences, each alone
+        r.forward([(seqs[i][:lens[i]], 0, i, pages[i], [lens[i] - 1])])
+    got = [[] for _ in seqs]
+    for t in range(steps):
+        ents = [([seqs[i][lens[i] + t]], lens[i] + t, i, pages[i], [0]) for i in range(3)]
+        lo, hi = 16 * t, (16 * (t + 1) if t < steps - 1 else len(seqs[3]))
+        ents.insert(1, (seqs[3][lo:hi], lo, 3, pages[3], list(range(hi - lo))))
+        lg, _ = r.forward(ents)
+        got[0].append(lg[0:1]); got[3].append(lg[1:1 + hi - lo]); got[1].append(lg[1 + hi - lo:2 + hi - lo]); got[2].append(lg[2 + hi - lo:])
+    for i in range(3):
+        assert U.rel_err(np.concatenate(got[i]), refs[i][lens[i]:]) < 2e-3, f"decoding sequence {i}"
+    assert U.rel_err(np.concatenate(got[3]), refs[3]) < 2e-3
+
+
 def test_first_tokens_and_long_decoding(tmp_path):
     cfg = U.config(FULL)
     r, plain, _ = _runner(tmp_path, cfg, seed=2)
