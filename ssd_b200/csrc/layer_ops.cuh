@@ -1,7 +1,7 @@
 // layer_ops.cuh — the element-wise steps of a layered (hybrid) model's block.  The residual stream, every norm
 // statistic and every gate are fp32; T (bf16 or float) is the storage type of the activations that feed a linear layer.
 //   embed_rows_kernel         x = embed[token]                                  (fp32 residual)
-//   unit_offset_rmsnorm_kernel y = x / sqrt(mean(x^2) + eps) * (1 + w)           (norm weight stored around zero)
+//   unit_offset_rmsnorm_kernel y = x / sqrt(mean(x^2) + eps) * (1 + w)           (unit-offset weight: the scale is 1 + w)
 //   token_shift_kernel        RWKV token shift: S mixes h + (h_prev - h) * mu_s, h_prev carried in the state slot
 //   head_rmsnorm_gate_kernel  per-head unit RMS, times a channel weight, times silu / sigmoid of a gate pre-activation
 //   clamped_glu_kernel        y = g * sigmoid(1.702 g) * (u + 1) with g = min(g, lim), u = clamp(u, -lim, lim)

@@ -1,7 +1,7 @@
 // moe.cuh — routing of a sigmoid-scored, group-limited mixture of experts.
 //
 //   group_topk_router_kernel  one warp per token.  scores = sigmoid(router logits) (fp32).  The experts form `groups`
-//       equal groups of neighbours; a group scores the sum of its two best experts (one, if a group has one expert);
+//       equal, contiguous groups; a group scores the sum of its two best experts (one, if a group has one expert);
 //       only experts of the `keep` best groups compete; the `top` best of those are chosen; their scores, divided by
 //       their sum (+ 1e-20) and multiplied by `route_scale`, are the combination weights.  Ties go to the lower index.
 //   expert_plan_kernel        one CTA: counting sort of the (token, k) assignments by expert -> for every assignment

@@ -19,7 +19,7 @@ def unit_rms(v: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 def block_norm(x, weight, eps):
-    """RMS norm whose weight is stored around zero."""
+    """RMS norm with a unit-offset weight (scale 1 + w)."""
     return unit_rms(x, eps) * (1.0 + weight)
 
 
