@@ -14,8 +14,8 @@
 //   attention proper     per sequence and query block, as two tensor-core GEMMs around a softmax (HybRun::latent):
 //                        latent_gather_kernel (pages -> contiguous keys and transposed latents), scores = Q K^T with the
 //                        (token, head) pairs as rows (every head meets the same keys: multi-query), sink_softmax_kernel
-//                        (fp32: causal edge per row, the sink as one more term of the denominator with no key and no
-//                        value), output = P C.  Accumulation runs over keys in index order, whatever the portion.
+//                        (fp32: causal edge per row; the per-head sink logit only enlarges the denominator, it
+//                        contributes nothing to the output), output = P C.  Accumulation runs over keys in index order, whatever the portion.
 //   single-token rows    (decode) skip the gather and the GEMMs: latent_decode_partial_kernel walks the pages of ALL such
 //                        sequences in one launch, split along the context (scores, running maximum and P C per split,
 //                        fp32), latent_decode_merge_kernel joins the splits and adds the sink to the denominator.
