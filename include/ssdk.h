@@ -262,8 +262,14 @@ int ssdk_verify(const void* logits_p, const void* logits_q, const int64_t* specu
  * Storage type T of weights / activations / latent cache: bf16 (fp32 accumulation; residual stream, norms, routers,
  * attention scores, gates and recurrent state in fp32) or fp32 throughout (no TF32). */
 enum { SSDK_DT_F32 = 0, SSDK_DT_BF16 = 1 };
-enum { SSDK_MIX_WKV = 0, SSDK_MIX_MLSTM = 1, SSDK_MIX_LATENT_ATTN = 2 };
-enum { SSDK_MLP_NONE = 0, SSDK_MLP_MOE = 1 };
+enum { SSDK_MIX_WKV = 0, SSDK_MIX_MLSTM = 1, SSDK_MIX_LATENT_ATTN = 2,
+       SSDK_MIX_RGLRU = 3,        /* gated diagonal linear recurrence behind a short convolution, times a gelu branch */
+       SSDK_MIX_SELECTIVE = 4,    /* selective scan (input-dependent step, B, C) behind a short convolution, silu gate */
+       SSDK_MIX_ATTN_DELTA = 5 }; /* grouped-query sink attention and a gated delta rule side by side on the same input */
+enum { SSDK_MLP_NONE = 0, SSDK_MLP_MOE = 1, SSDK_MLP_GLU = 2 /* dense: down(gelu_tanh(gate h) * (up h)) */ };
+/* how a layer joins the residual stream */
+enum { SSDK_BLOCK_PARALLEL_PRENORM = 0,  /* x += ls1 * mixer(h) + ls2 * ff(h), h = norm(x) */
+       SSDK_BLOCK_SERIAL_POSTNORM = 1 }; /* x += m * norm1(mixer(x)); x += m * norm2(ff(x)): the sublayers read x itself */
 
 /* tensors of a hybrid model (ssdk_hyb_bind); [out, in] row-major, storage type T */
 enum {
@@ -300,6 +306,32 @@ enum {
   SSDK_HT_EXPERT_OUT,    /* [E, width, ff] */
   SSDK_HT_SHARED_IN,     /* [2 sff + 1, width]: gate | up | shared-gate row */
   SSDK_HT_SHARED_OUT,    /* [width, sff] */
+  /* serial post-norm blocks */
+  SSDK_HT_NORM2,         /* [width] norm on the feed-forward's output */
+  SSDK_HT_GLU_IN,        /* [2 ff, width]: gate rows then up rows */
+  SSDK_HT_GLU_OUT,       /* [width, ff] */
+  /* short convolutions of the recurrent mixers */
+  SSDK_HT_CONV_W,        /* [channels, taps], the last column multiplies the current token */
+  SSDK_HT_CONV_B,        /* [channels] or unbound */
+  /* rglru */
+  SSDK_HT_RGLRU_IN,      /* [2 R, width]: y-branch rows then x-branch rows */
+  SSDK_HT_RGLRU_IN_B,    /* [2 R] their biases */
+  SSDK_HT_RGLRU_GATE,    /* [blocks, 2 bs, bs]: per block the recurrence-gate rows then the input-gate rows */
+  SSDK_HT_RGLRU_GATE_B,  /* [blocks, 2 bs] */
+  SSDK_HT_RGLRU_LAM,     /* [R] */
+  /* selective scan */
+  SSDK_HT_SEL_IN,        /* [2 inner, width]: x rows then z rows */
+  SSDK_HT_SEL_X,         /* [dt_rank + 2 state, inner] */
+  SSDK_HT_SEL_DT,        /* [inner, dt_rank] */
+  SSDK_HT_SEL_DT_B,      /* [inner] */
+  SSDK_HT_SEL_ALOG,      /* [inner, state] */
+  SSDK_HT_SEL_D,         /* [inner] */
+  /* attention + delta rule pair: ONE stacked input projection,
+   * rows: attn q [H D] | k [G D] | v [G V] | gate [H V] | delta q [Gd Dd] | k [Gd Dd] | v [Hd Vd] | gate [Hd Vd] | beta [Hd] | a [Hd] */
+  SSDK_HT_PAIR_IN,
+  SSDK_HT_ATTN_OUT,      /* [width, H V] */
+  SSDK_HT_DELTA_ALOG,    /* [Hd] */
+  SSDK_HT_DELTA_DT_B,    /* [Hd] */
   SSDK_HT_COUNT
 };
 
@@ -314,6 +346,20 @@ typedef struct ssdk_hyb_layer_cfg {
   int32_t experts, top, groups, keep;
   int32_t ff, shared_ff;             /* shared_ff = 0: no shared expert */
   float   route_scale, limit, shared_limit;
+  /* grouped-query attention (SSDK_MIX_ATTN_DELTA uses heads / dim / vdim / rot_dims / rot_base / attn_scale above) */
+  int32_t kv_heads;                  /* key/value heads; query head h reads head h / (heads / kv_heads) */
+  int32_t qk_norm;                   /* 1: q and k divided by their RMS over dim after the rotation */
+  float   sink;                      /* constant added to the softmax denominator (0: plain softmax; 1: a sink of score 0) */
+  float   yarn_factor;               /* 0: no frequency scaling; else YaRN with the three values below */
+  float   yarn_original, yarn_fast, yarn_slow;
+  /* short convolution (rglru, selective scan, delta rule) */
+  int32_t conv;                      /* taps */
+  /* rglru: `inner` channels in `blocks` gate blocks; selective scan: inner x state, dt_rank */
+  int32_t inner, blocks, state, dt_rank;
+  float   decay_mult;                /* rglru: log a = -decay_mult * r * softplus(lam) */
+  /* gated delta rule of SSDK_MIX_ATTN_DELTA */
+  int32_t d_heads, d_kv_heads, d_dim, d_vdim;
+  float   left_scale, right_scale;   /* result = left_scale * attention + right_scale * delta rule */
 } ssdk_hyb_layer_cfg;
 
 typedef struct ssdk_hyb_cfg {
@@ -323,7 +369,10 @@ typedef struct ssdk_hyb_cfg {
   int32_t max_seqs;          /* sequences per forward call */
   int32_t max_logit_rows;    /* rows whose logits one call can return */
   int32_t block_size, max_blocks_per_seq;
-  int32_t reserved;
+  int32_t block;             /* SSDK_BLOCK_* */
+  float   norm_offset;       /* a norm scales by norm_offset + w: 1 for unit-offset weights, 0 for plain ones */
+  float   embed_scale;       /* x = embed[token] * embed_scale */
+  float   residual_mult;     /* m of SSDK_BLOCK_SERIAL_POSTNORM */
 } ssdk_hyb_cfg;
 
 typedef struct ssdk_hyb_engine* ssdk_hyb_handle;
@@ -331,8 +380,8 @@ typedef struct ssdk_hyb_engine* ssdk_hyb_handle;
 int ssdk_hyb_create(const ssdk_hyb_cfg* cfg, const ssdk_hyb_layer_cfg* layers, ssdk_hyb_handle* out);
 int ssdk_hyb_destroy(ssdk_hyb_handle h);
 int ssdk_hyb_bind(ssdk_hyb_handle h, int layer, int tensor, const void* dev_ptr, int64_t rows, int64_t cols);
-/* caller-owned pools: latent cache (per latent-attention layer [num_blocks, block_size, kv_rank + rot_dim] T, layers
- * back to back), recurrent state (fp32, n_slots slots), workspace */
+/* caller-owned pools: paged cache (per latent-attention layer [num_blocks, block_size, kv_rank + rot_dim] T, per
+ * grouped-query attention layer [num_blocks, block_size, G (D + V)] T: keys of all heads, then values; layers back to back), recurrent state (fp32, n_slots slots), workspace */
 int64_t ssdk_hyb_cache_bytes(ssdk_hyb_handle h, int64_t num_blocks);
 int64_t ssdk_hyb_state_bytes(ssdk_hyb_handle h, int64_t n_slots);
 int64_t ssdk_hyb_workspace_bytes(ssdk_hyb_handle h);

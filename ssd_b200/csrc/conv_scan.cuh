@@ -1,0 +1,345 @@
+// conv_scan.cuh — recurrent mixers that sit behind a short causal convolution, for the layered (hybrid) models.
+// Everything here is fp32: the convolution, its activation, gates, decays, step sizes and the carried state; T (bf16 or
+// float) is only the storage type of weights and of the rows handed to the next linear layer.
+//
+//   short_conv_kernel     per-channel causal convolution over time (taps from the checkpoint, last tap = current token),
+//                         optional input bias / output bias / SiLU; rows before the portion come from the state slot,
+//                         zeros before the sequence
+//   conv_state_kernel     saves the last taps - 1 inputs of every sequence's portion into its slot (runs after the readers)
+//   rglru_scan_kernel     S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t,  a_t = exp(-c r_t softplus(lam)),  out = S_t gelu(y_t)
+//   selective_scan_kernel S[c,n] = exp(dt_c A[c,n]) S[c,n] + dt_c x_c B_n,  y_c = sum_n S[c,n] C_n + D_c x_c,  out = y silu(z)
+//   delta_prep_kernel     convolution + SiLU of q | k | v, unit vectors per head for q and k, beta and the head decay
+//   delta_scan_kernel     gated delta rule: S = g S; u = beta (v - S^T k); S += k u^T; o = S^T q
+//
+// A state slot is never cleared: a sequence whose portion starts at position 0 ignores what the slot holds.
+#pragma once
+#include "layer_ops.cuh"
+
+namespace ssdk {
+
+SSDK_DEVINL float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+SSDK_DEVINL float silu_f(float z) { return z * sigmoid_f(z); }
+SSDK_DEVINL float gelu_tanh_f(float z) { return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
+
+struct ConvArgs {
+  const float* in;      // [M, ld_in] rows before the convolution; channel c is column c
+  int ld_in;
+  const void* in_bias;  // [C] T added to every input row (not to the zeros before the sequence), or nullptr
+  const void* w;        // [C, taps] T
+  const void* bias;     // [C] T added to the result, or nullptr
+  float* out;           // [M, ld_out] fp32, or nullptr
+  int ld_out;
+  void* out_t;          // [M, ld_t] T copy for a following linear layer, or nullptr
+  int ld_t;
+  float* hist;          // state: [taps - 1, C] per slot (with the input bias already added), oldest first
+  size_t slot_stride;
+  int C, taps;
+};
+
+// value of channel c at row m (row t of sequence s) after the convolution, before any activation
+template <typename T>
+SSDK_DEVINL float conv_at(const ConvArgs& p, const Ragged& rg, int m, int s, int t, int c) {
+  float acc = p.bias ? ld_f<T>((const T*)p.bias + c) : 0.f;
+  const float ib = p.in_bias ? ld_f<T>((const T*)p.in_bias + c) : 0.f;
+  const bool carried = rg.pos0[s] > 0;
+  const float* hist = p.hist + (size_t)rg.slot[s] * p.slot_stride;
+  for (int j = 0; j < p.taps; ++j) {
+    const int back = p.taps - 1 - j;
+    float v;
+    if (back <= t) v = p.in[(size_t)(m - back) * p.ld_in + c] + ib;
+    else v = carried ? hist[(size_t)(p.taps - 1 - (back - t)) * p.C + c] : 0.f;
+    acc = fmaf(ld_f<T>((const T*)p.w + (size_t)c * p.taps + j), v, acc);
+  }
+  return acc;
+}
+
+// ACT: 0 none, 1 SiLU.  grid (M, ceil(C / blockDim))
+template <typename T, int ACT>
+__global__ void short_conv_kernel(const ConvArgs p, const Ragged rg) {
+  const int m = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= p.C) return;
+  const int s = rg.tok_seq[m];
+  float v = conv_at<T>(p, rg, m, s, m - rg.cu[s], c);
+  if (ACT == 1) v = silu_f(v);
+  if (p.out) p.out[(size_t)m * p.ld_out + c] = v;
+  if (p.out_t) st_f<T>((T*)p.out_t + (size_t)m * p.ld_t + c, v);
+}
+
+// grid (n_seqs, ceil(C / blockDim)).  New history = the last taps - 1 entries of (old history ++ this portion's inputs);
+// entry j is read from an index above j, so one thread per channel may work in place in ascending order.
+template <typename T>
+__global__ void conv_state_kernel(const ConvArgs p, const Ragged rg) {
+  const int s = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= p.C) return;
+  const int r0 = rg.cu[s], n = rg.cu[s + 1] - r0, keep = p.taps - 1;
+  const bool carried = rg.pos0[s] > 0;
+  const float ib = p.in_bias ? ld_f<T>((const T*)p.in_bias + c) : 0.f;
+  float* hist = p.hist + (size_t)rg.slot[s] * p.slot_stride;
+  for (int j = 0; j < keep; ++j) {
+    const int idx = n + j;
+    float v;
+    if (idx < keep) v = carried ? hist[(size_t)idx * p.C + c] : 0.f;
+    else v = p.in[(size_t)(r0 + idx - keep) * p.ld_in + c] + ib;
+    hist[(size_t)j * p.C + c] = v;
+  }
+}
+
+// fp32 columns -> T columns (operand of a following linear layer)
+template <typename T>
+__global__ void cast_cols_kernel(const float* __restrict__ src, int ld_src, T* __restrict__ dst, int ld_dst, int cols) {
+  const int m = blockIdx.x;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) st_f<T>(dst + (size_t)m * ld_dst + c, src[(size_t)m * ld_src + c]);
+}
+
+// ---------------------------------------------------------------------------------------------- rglru
+struct RglruArgs {
+  const float* u; int ld_u;          // [M, R] convolved x branch
+  const float* gates; int ld_g;      // [M, blocks * 2 bs]: per block recurrence-gate pre-activations, then input-gate ones
+  const void* gate_bias;             // [blocks, 2 bs] T
+  const void* lam;                   // [R] T
+  const float* y; int ld_y;          // [M, ...] y-branch pre-activation without its bias
+  const void* y_bias;                // [R] T
+  void* out;                         // [M, R] T: S * gelu_tanh(y)
+  float* S; size_t slot_stride;      // [R] per slot
+  int R, bs;
+  float decay_mult;
+};
+
+// grid (n_seqs, ceil(R / blockDim)): one thread per channel walks its sequence's rows
+template <typename T>
+__global__ void rglru_scan_kernel(const RglruArgs p, const Ragged rg) {
+  const int s = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= p.R) return;
+  const int b = c / p.bs, cb = c - b * p.bs;
+  const int gr = b * 2 * p.bs + cb, gi = gr + p.bs;
+  const float rb = ld_f<T>((const T*)p.gate_bias + gr), ib = ld_f<T>((const T*)p.gate_bias + gi);
+  const float sp = softplus_f(ld_f<T>((const T*)p.lam + c)) * p.decay_mult;
+  const float yb = ld_f<T>((const T*)p.y_bias + c);
+  float* Sp = p.S + (size_t)rg.slot[s] * p.slot_stride + c;
+  float S = rg.pos0[s] > 0 ? *Sp : 0.f;
+  const int r0 = rg.cu[s], r1 = rg.cu[s + 1];
+  for (int m = r0; m < r1; ++m) {
+    const float r = sigmoid_f(p.gates[(size_t)m * p.ld_g + gr] + rb);
+    const float i = sigmoid_f(p.gates[(size_t)m * p.ld_g + gi] + ib);
+    const float log_a = -r * sp;
+    const float a = expf(log_a);
+    // 1 - a^2 through expm1: exact also where a is within an ulp of 1
+    S = fmaf(a, S, sqrtf(-expm1f(2.0f * log_a)) * i * p.u[(size_t)m * p.ld_u + c]);
+    st_f<T>((T*)p.out + (size_t)m * p.R + c, S * gelu_tanh_f(p.y[(size_t)m * p.ld_y + c] + yb));
+  }
+  *Sp = S;
+}
+
+// ---------------------------------------------------------------------------------------------- selective scan
+struct SelScanArgs {
+  const float* x; int ld_x;          // [M, inner] convolved, SiLU'd input
+  const float* dtz; int ld_dt;       // [M, inner] step-size pre-activation without its bias
+  const void* dt_bias;               // [inner] T
+  const float* bc; int ld_bc;        // [M, ...]: B in columns [0, N), C in [N, 2N)
+  const void* A_log;                 // [inner, N] T
+  const void* Dw;                    // [inner] T
+  const float* z; int ld_z;          // [M, inner] gate pre-activation
+  void* out;                         // [M, inner] T: y * silu(z)
+  float* S; size_t slot_stride;      // [inner, N] per slot
+  int inner, N;
+};
+
+constexpr int kSelRows = 8;  // rows whose B | C are staged together
+
+// grid (n_seqs, ceil(inner / blockDim)).  NT > 0: the channel's N <= NT states live in registers; NT == 0: any N, the
+// state stays in its slot (global memory).  dynamic shared memory: kSelRows * 2 N floats.
+template <typename T, int NT>
+__global__ void selective_scan_kernel(const SelScanArgs p, const Ragged rg) {
+  extern __shared__ float sel_sm[];
+  const int s = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x, N = p.N;
+  const bool live = c < p.inner;
+  const bool carried = rg.pos0[s] > 0;
+  float A[NT > 0 ? NT : 1], S[NT > 0 ? NT : 1];
+  float* Sg = p.S + (size_t)rg.slot[s] * p.slot_stride + (size_t)(live ? c : 0) * N;
+  if (NT > 0) {
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      A[n] = (live && n < N) ? -expf(ld_f<T>((const T*)p.A_log + (size_t)c * N + n)) : 0.f;
+      S[n] = (live && n < N && carried) ? Sg[n] : 0.f;
+    }
+  } else if (live && !carried) {
+    for (int n = 0; n < N; ++n) Sg[n] = 0.f;
+  }
+  const float dtb = live ? ld_f<T>((const T*)p.dt_bias + c) : 0.f, Dc = live ? ld_f<T>((const T*)p.Dw + c) : 0.f;
+  const int r0 = rg.cu[s], r1 = rg.cu[s + 1];
+  for (int m0 = r0; m0 < r1; m0 += kSelRows) {
+    const int nr = min(kSelRows, r1 - m0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nr * 2 * N; i += blockDim.x) {
+      const int r = i / (2 * N), k = i - r * 2 * N;
+      sel_sm[i] = p.bc[(size_t)(m0 + r) * p.ld_bc + k];
+    }
+    __syncthreads();
+    if (!live) continue;
+    for (int r = 0; r < nr; ++r) {
+      const int m = m0 + r;
+      const float dt = softplus_f(p.dtz[(size_t)m * p.ld_dt + c] + dtb);
+      const float xv = p.x[(size_t)m * p.ld_x + c], dx = dt * xv;
+      const float* B = sel_sm + r * 2 * N;
+      const float* Cm = B + N;
+      float y = 0.f;
+      if (NT > 0) {
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+          if (n < N) {
+            S[n] = fmaf(expf(dt * A[n]), S[n], dx * B[n]);
+            y = fmaf(S[n], Cm[n], y);
+          }
+        }
+      } else {
+        for (int n = 0; n < N; ++n) {
+          const float a = -expf(ld_f<T>((const T*)p.A_log + (size_t)c * N + n));
+          const float sn = fmaf(expf(dt * a), Sg[n], dx * B[n]);
+          Sg[n] = sn;
+          y = fmaf(sn, Cm[n], y);
+        }
+      }
+      y = fmaf(Dc, xv, y);
+      st_f<T>((T*)p.out + (size_t)m * p.inner + c, y * silu_f(p.z[(size_t)m * p.ld_z + c]));
+    }
+  }
+  if (NT > 0 && live) {
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+      if (n < N) Sg[n] = S[n];
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- gated delta rule
+struct DeltaPrepArgs {
+  ConvArgs conv;          // over the q | k | v columns (C = 2 G D + H V); out / out_t unused
+  const float* ba; int ld_ba;  // [M, ...]: beta pre-activations in columns [0, H), decay pre-activations in [H, 2H)
+  const void* A_log;      // [H] T
+  const void* dt_bias;    // [H] T
+  float* q;               // [M, G D] unit vectors * q_scale
+  float* k;               // [M, G D] unit vectors
+  float* v;               // [M, H V]
+  float* beta;            // [M, H]
+  float* decay;           // [M, H]
+  int H, G, D, V;
+  float q_scale, unit_eps;
+};
+
+// grid (M); dynamic shared memory: (2 G D + H V) floats
+template <typename T>
+__global__ void delta_prep_kernel(const DeltaPrepArgs p, const Ragged rg) {
+  extern __shared__ float dp_sm[];
+  const int m = blockIdx.x, s = rg.tok_seq[m], t = m - rg.cu[s];
+  const int GD = p.G * p.D, HV = p.H * p.V, C = 2 * GD + HV;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) dp_sm[c] = silu_f(conv_at<T>(p.conv, rg, m, s, t, c));
+  for (int h = threadIdx.x; h < p.H; h += blockDim.x) {
+    p.beta[(size_t)m * p.H + h] = sigmoid_f(p.ba[(size_t)m * p.ld_ba + h]);
+    const float sp = softplus_f(p.ba[(size_t)m * p.ld_ba + p.H + h] + ld_f<T>((const T*)p.dt_bias + h));
+    p.decay[(size_t)m * p.H + h] = expf(-expf(ld_f<T>((const T*)p.A_log + h)) * sp);
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < HV; c += blockDim.x) p.v[(size_t)m * HV + c] = dp_sm[2 * GD + c];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int unit = warp; unit < 2 * p.G; unit += nw) {  // units 0 .. G-1: query heads, G .. 2G-1: key heads
+    const float* src = dp_sm + (size_t)unit * p.D;
+    float ss = 0.f;
+    for (int d = lane; d < p.D; d += 32) ss = fmaf(src[d], src[d], ss);
+    ss = warp_sum(ss);
+    const bool is_q = unit < p.G;
+    const float inv = (is_q ? p.q_scale : 1.0f) / sqrtf(ss + p.unit_eps);
+    float* dst = (is_q ? p.q : p.k) + (size_t)m * GD + (size_t)(is_q ? unit : unit - p.G) * p.D;
+    for (int d = lane; d < p.D; d += 32) dst[d] = src[d] * inv;
+  }
+}
+
+struct DeltaArgs {
+  const float* q; const float* k;    // [M, G D]
+  const float* v;                    // [M, H V]
+  const float* beta; const float* decay;  // [M, H]
+  float* o;                          // [M, H V]
+  float* S; size_t slot_stride;      // [H, D, V] per slot
+  int H, G, D, V;
+};
+
+constexpr int kDeltaRows = 8;  // rows staged together
+
+inline size_t delta_scan_smem(int D, int Vr, int DR) {
+  const int DP = DR > 0 ? DR : D;
+  return ((size_t)(DR > 0 ? 0 : D * Vr) + (size_t)kDeltaRows * (2 * DP + Vr + 2)) * 4;
+}
+
+// grid (n_seqs, H), blockDim = V rounded up to a warp: thread j owns column j of the head's D x V state, so both
+// contractions over D (S^T k and S^T q) are thread-local sums in row order and the walk needs no reduction across
+// threads.  DR > 0: the column lives in registers (D <= DR, padded rows meet k = q = 0); DR == 0: in shared memory.
+template <typename T, int DR>
+__global__ void delta_scan_kernel(const DeltaArgs p, const Ragged rg) {
+  extern __shared__ float ds_sm[];
+  const int s = blockIdx.x, hd = blockIdx.y, g = hd / (p.H / p.G), j = threadIdx.x, Vr = blockDim.x;
+  const int D = p.D, V = p.V, DP = DR > 0 ? DR : D;
+  float* Ssm = ds_sm;                                     // [D][Vr] (DR == 0)
+  float* kq = ds_sm + (DR > 0 ? 0 : (size_t)D * Vr);      // [rows][2 DP]: k then q
+  float* vs = kq + kDeltaRows * 2 * DP;                   // [rows][Vr]
+  float* bg = vs + kDeltaRows * Vr;                       // [rows][2]: beta, decay
+  float Sr[DR > 0 ? DR : 1];
+  const bool col = j < V, carried = rg.pos0[s] > 0;
+  float* Sg = p.S + (size_t)rg.slot[s] * p.slot_stride + (size_t)hd * D * V + (col ? j : 0);
+  if (DR > 0) {
+#pragma unroll
+    for (int d = 0; d < DR; ++d) Sr[d] = (col && carried && d < D) ? Sg[(size_t)d * V] : 0.f;
+  } else {
+    for (int d = 0; d < D; ++d) Ssm[(size_t)d * Vr + j] = (col && carried) ? Sg[(size_t)d * V] : 0.f;
+  }
+  const int r0 = rg.cu[s], r1 = rg.cu[s + 1], GD = p.G * D, HV = p.H * V;
+  for (int m0 = r0; m0 < r1; m0 += kDeltaRows) {
+    const int nr = min(kDeltaRows, r1 - m0);
+    __syncthreads();
+    for (int i = j; i < nr * DP; i += Vr) {
+      const int r = i / DP, d = i - r * DP;
+      kq[r * 2 * DP + d] = d < D ? p.k[(size_t)(m0 + r) * GD + g * D + d] : 0.f;
+      kq[r * 2 * DP + DP + d] = d < D ? p.q[(size_t)(m0 + r) * GD + g * D + d] : 0.f;
+    }
+    for (int r = 0; r < nr; ++r) vs[r * Vr + j] = col ? p.v[(size_t)(m0 + r) * HV + hd * V + j] : 0.f;
+    if (j < nr) {
+      bg[2 * j] = p.beta[(size_t)(m0 + j) * p.H + hd];
+      bg[2 * j + 1] = p.decay[(size_t)(m0 + j) * p.H + hd];
+    }
+    __syncthreads();
+    for (int r = 0; r < nr; ++r) {
+      const float* kr = kq + r * 2 * DP;
+      const float* qr = kr + DP;
+      const float beta = bg[2 * r], dec = bg[2 * r + 1];
+      float dot = 0.f, o = 0.f;
+      if (DR > 0) {
+#pragma unroll
+        for (int d = 0; d < DR; ++d) { Sr[d] *= dec; dot = fmaf(Sr[d], kr[d], dot); }
+        const float u = beta * (vs[r * Vr + j] - dot);
+#pragma unroll
+        for (int d = 0; d < DR; ++d) { Sr[d] = fmaf(kr[d], u, Sr[d]); o = fmaf(Sr[d], qr[d], o); }
+      } else {
+        for (int d = 0; d < D; ++d) {
+          const float sv = Ssm[(size_t)d * Vr + j] * dec;
+          Ssm[(size_t)d * Vr + j] = sv;
+          dot = fmaf(sv, kr[d], dot);
+        }
+        const float u = beta * (vs[r * Vr + j] - dot);
+        for (int d = 0; d < D; ++d) {
+          const float sv = fmaf(kr[d], u, Ssm[(size_t)d * Vr + j]);
+          Ssm[(size_t)d * Vr + j] = sv;
+          o = fmaf(sv, qr[d], o);
+        }
+      }
+      if (col) p.o[(size_t)(m0 + r) * HV + hd * V + j] = o;
+    }
+  }
+  if (col) {
+    if (DR > 0) {
+#pragma unroll
+      for (int d = 0; d < DR; ++d)
+        if (d < D) Sg[(size_t)d * V] = Sr[d];
+    } else {
+      for (int d = 0; d < D; ++d) Sg[(size_t)d * V] = Ssm[(size_t)d * Vr + j];
+    }
+  }
+}
+
+}  // namespace ssdk

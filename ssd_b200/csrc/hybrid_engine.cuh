@@ -3,6 +3,8 @@
 // tokens share.  Included by engine.cu; uses its Launcher / error helpers.  Kernels: layer_ops.cuh, linear.cuh,
 // recurrent.cuh, latent_attention.cuh, moe.cuh; the sampler is sample_kernel of sampling.cuh.
 #pragma once
+#include "conv_scan.cuh"
+#include "gqa_attention.cuh"
 #include "latent_attention.cuh"
 #include "layer_ops.cuh"
 #include "linear.cuh"
@@ -20,6 +22,7 @@ struct HybLayer {
   size_t cache_row = 0;      // row width (elements) of this layer's latent pool
   size_t cache_rows_before = 0;  // sum of the row widths of the latent layers before this one
   float* inv_freq = nullptr; // device, [rot_dims / 2]
+  float rot_mult = 1.0f;     // factor on cos and sin (frequency scaling)
 };
 
 struct ssdk_hyb_engine {
@@ -32,7 +35,7 @@ struct ssdk_hyb_engine {
   float* state = nullptr; int64_t n_slots = 0;
   // workspace carve
   int64_t ws_bytes = 0;
-  float *x = nullptr, *p0 = nullptr, *p1 = nullptr, *p2 = nullptr, *mix_out = nullptr;
+  float *x = nullptr, *p0 = nullptr, *p1 = nullptr, *p2 = nullptr, *mix_out = nullptr, *mix2 = nullptr;
   void *h = nullptr, *mixes = nullptr, *t0 = nullptr, *t1 = nullptr;
   // latent attention: concatenated queries, one sequence's gathered keys / transposed latents, score and weight blocks
   void *qcat = nullptr, *keys = nullptr, *lat_t = nullptr, *att_p = nullptr; float* att_s = nullptr;
@@ -46,7 +49,7 @@ struct ssdk_hyb_engine {
   int max_tiles = 0;
   // widths of the shared buffers (elements per row)
   int w_p0 = 0, w_p1 = 0, w_p2 = 0, w_t0 = 0, w_t1 = 0, w_e = 0, w_top = 0, w_ff2 = 0, w_ff = 0, w_sff2 = 0, w_sff = 0;
-  bool any_wkv = false;
+  bool any_wkv = false, any_pair = false;
   int* h_meta = nullptr;     // pinned staging of the step's integers
   // tcgen05 path of the dense bf16 products: TMA descriptors by (pointer, rows, K, box rows), split-K partials
   bool use_tc = true;
@@ -96,10 +99,43 @@ static int hyb_derive(ssdk_hyb_engine* e) {
       up(e->w_qcat, (long long)H * (c.kv_rank + c.rot_dim)); up(e->w_key, (long long)c.kv_rank + c.rot_dim);
       up(e->w_kr, c.kv_rank); up(e->w_lh, H);
       up(e->w_t0, std::max((long long)c.q_rank, (long long)H * c.kv_rank)); up(e->w_t1, std::max((long long)H * D, (long long)H * V));
+    } else if (c.mixer == SSDK_MIX_RGLRU) {
+      const int R = c.inner;
+      if (R < 1 || c.blocks < 1 || R % c.blocks || c.conv < 1) return fail("rglru: %d channels in %d blocks, %d taps", R, c.blocks, c.conv);
+      soff += (size_t)R + (size_t)(c.conv - 1) * R;
+      up(e->w_p0, 2LL * R); up(e->w_p1, R); up(e->w_p2, 2LL * R); up(e->w_t0, R); up(e->w_t1, R);
+    } else if (c.mixer == SSDK_MIX_SELECTIVE) {
+      const int I = c.inner, N = c.state, Rk = c.dt_rank;
+      if (I < 1 || N < 1 || Rk < 1 || c.conv < 1) return fail("selective scan: inner %d, state %d, dt rank %d, %d taps", I, N, Rk, c.conv);
+      soff += (size_t)I * N + (size_t)(c.conv - 1) * I;
+      up(e->w_p0, 2LL * I); up(e->w_p1, I); up(e->w_p2, (long long)Rk + 2 * N + I); up(e->w_t0, I); up(e->w_t1, std::max(I, Rk));
+    } else if (c.mixer == SSDK_MIX_ATTN_DELTA) {
+      const int G = c.kv_heads, Hd = c.d_heads, Gd = c.d_kv_heads, Dd = c.d_dim, Vd = c.d_vdim;
+      if (V < 1 || G < 1 || H % G) return fail("attention: %d query heads on %d key/value heads", H, G);
+      if (c.rot_dims < 0 || c.rot_dims > D || (c.rot_dims & 1)) return fail("attention: rot dims %d of %d", c.rot_dims, D);
+      if (V > 256 * 4) return fail("attention: value size %d too large", V);
+      if (Hd < 1 || Gd < 1 || Hd % Gd || Dd < 1 || Vd < 1 || Vd > 1024 || c.conv < 1)
+        return fail("delta rule: %d heads on %d query/key heads, %d x %d, %d taps", Hd, Gd, Dd, Vd, c.conv);
+      if (Dd > 128 && ssdk::delta_scan_smem(Dd, (Vd + 31) / 32 * 32, 0) > 200 * 1024) return fail("delta rule: head %d x %d too large", Dd, Vd);
+      const long long Cd = 2LL * Gd * Dd + (long long)Hd * Vd;
+      soff += (size_t)Hd * Dd * Vd + (size_t)(c.conv - 1) * Cd;
+      L.cache_row = (size_t)G * (D + V);
+      L.cache_rows_before = crow;
+      crow += L.cache_row;
+      up(e->w_p0, (long long)H * D + (long long)G * D + (long long)G * V + (long long)H * V + Cd + (long long)Hd * Vd + 2 * Hd);
+      up(e->w_p1, std::max((long long)H * V, (long long)Hd * Vd)); up(e->w_p2, Cd + 2 * Hd);
+      up(e->w_t0, (long long)H * V); up(e->w_t1, (long long)Hd * Vd);
+      up(e->w_qcat, (long long)H * D); up(e->w_key, (long long)G * D); up(e->w_kr, (long long)G * V); up(e->w_lh, H);
+      e->any_pair = true;
     } else {
       return fail("hybrid layer: unknown mixer %d", c.mixer);
     }
-    if (c.mlp == SSDK_MLP_MOE) {
+    if (c.mlp == SSDK_MLP_GLU) {
+      if (c.ff < 1) return fail("dense feed-forward: ff %d", c.ff);
+      if (e->cfg.block != SSDK_BLOCK_SERIAL_POSTNORM) return fail("the dense feed-forward is built for serial blocks");
+      up(e->w_p0, 2LL * c.ff); up(e->w_t0, c.ff);
+    } else if (c.mlp == SSDK_MLP_MOE) {
+      if (e->cfg.block != SSDK_BLOCK_PARALLEL_PRENORM) return fail("the mixture of experts is built for parallel blocks");
       if (c.experts < 1 || c.experts > kRouterMaxE) return fail("moe: 1 <= experts <= %d", kRouterMaxE);
       if (c.groups < 1 || c.experts % c.groups) return fail("moe: %d experts do not form %d equal groups", c.experts, c.groups);
       if (c.keep < 1 || c.keep > c.groups) return fail("moe: keep %d of %d groups", c.keep, c.groups);
@@ -130,6 +166,7 @@ static int64_t hyb_carve(ssdk_hyb_engine* e, uint8_t* base) {
   e->t0 = take(cap * e->w_t0 * es);
   e->t1 = take(cap * e->w_t1 * es);
   e->mix_out = (float*)take(cap * g.width * 4);
+  e->mix2 = (float*)take(e->any_pair ? cap * g.width * 4 : 0);
   {
     const size_t ctx_pad = align_up((size_t)g.max_blocks_per_seq * g.block_size, 8);
     e->qcat = take(cap * e->w_qcat * es);
@@ -397,7 +434,7 @@ struct HybRun {
         const T* qrows = (const T*)e->qcat + (size_t)(r0 + q0) * H * Wd;
         CKI(lin(qrows, Wd, e->keys, Wd, e->att_s, cb, rows, cb, Wd, false, 1, 0, 0, 0, false));
         CKI(L.go(ssdk::sink_softmax_kernel<T>, dim3(rows), dim3(256), 0, (const float*)e->att_s, (T*)e->att_p,
-                 (const T*)Lr.t[SSDK_HT_LAT_SINK].p, H, cb, p0 + q0, c.attn_scale));
+                 (const T*)Lr.t[SSDK_HT_LAT_SINK].p, H, cb, p0 + q0, c.attn_scale, rows, 0.f));
         CKI(lin(e->att_p, cb, e->lat_t, ctx_pad, (T*)e->t0 + (size_t)(r0 + q0) * H * KR, KR, rows, KR, cb, true, 1, 0, 0, 0, false));
       }
     }
@@ -439,14 +476,220 @@ struct HybRun {
     return 0;
   }
 
+  // ---- mixers of the serial post-norm designs (usable in either block kind: they read `hin`) ----
+  const void* hin = nullptr;   // the sublayer's input in the storage type: normed rows (parallel blocks) or x itself
+  static constexpr bool kF32 = std::is_same<T, float>::value;
+  const T* w_at(const HybTensor& t, size_t off) const { return (const T*)t.p + off; }
+
+  int glu(HybLayer& Lr) {
+    const int W = e->cfg.width, ff = Lr.c.ff;
+    CKI(check_tensor(Lr, SSDK_HT_GLU_IN, 2 * ff, W, "mlp.gate|up")); CKI(check_tensor(Lr, SSDK_HT_GLU_OUT, W, ff, "mlp.down"));
+    CKI(lin(hin, W, Lr.t[SSDK_HT_GLU_IN].p, W, e->p0, 2 * ff, M, 2 * ff, W));
+    CKI(L.go(ssdk::glu_act_kernel<T>, dim3(M), dim3(256), 0, (const float*)e->p0, 2 * ff, (T*)e->t0, ff));
+    return lin(e->t0, ff, Lr.t[SSDK_HT_GLU_OUT].p, ff, e->mix_out, W, M, W, ff);
+  }
+
+  int rglru(HybLayer& Lr) {
+    const ssdk_hyb_layer_cfg& c = Lr.c;
+    const int W = e->cfg.width, R = c.inner, nb = c.blocks, bs = R / nb, taps = c.conv;
+    CKI(check_tensor(Lr, SSDK_HT_RGLRU_IN, 2 * R, W, "rglru.y|x")); CKI(check_tensor(Lr, SSDK_HT_RGLRU_IN_B, 2 * R, 1, "rglru.y.b|x.b"));
+    CKI(check_tensor(Lr, SSDK_HT_CONV_W, R, taps, "conv")); CKI(check_tensor(Lr, SSDK_HT_CONV_B, R, 1, "conv.b"));
+    CKI(check_tensor(Lr, SSDK_HT_RGLRU_GATE, (int64_t)nb * 2 * bs, bs, "rglru.ra|ri"));
+    CKI(check_tensor(Lr, SSDK_HT_RGLRU_GATE_B, (int64_t)nb * 2 * bs, 1, "rglru.ra.b|ri.b"));
+    CKI(check_tensor(Lr, SSDK_HT_RGLRU_LAM, R, 1, "rglru.lam")); CKI(check_tensor(Lr, SSDK_HT_MIX_OUT, W, R, "mix.o"));
+    CKI(lin(hin, W, Lr.t[SSDK_HT_RGLRU_IN].p, W, e->p0, 2 * R, M, 2 * R, W));   // y pre-activations | x branch
+    float* st = e->state + Lr.state_off;
+    ssdk::ConvArgs ca = {};
+    ca.in = e->p0 + R; ca.ld_in = 2 * R; ca.in_bias = w_at(Lr.t[SSDK_HT_RGLRU_IN_B], R); ca.w = Lr.t[SSDK_HT_CONV_W].p;
+    ca.bias = Lr.t[SSDK_HT_CONV_B].p; ca.out = e->p1; ca.ld_out = R; ca.out_t = kF32 ? nullptr : e->t0; ca.ld_t = R;
+    ca.hist = st + R; ca.slot_stride = e->slot_floats; ca.C = R; ca.taps = taps;
+    const dim3 cgrid(M, (R + 255) / 256), sgrid(rg.n_seqs, (R + 255) / 256);
+    CKI(L.go(ssdk::short_conv_kernel<T, 0>, cgrid, dim3(256), 0, ca, rg));
+    CKI(L.go(ssdk::conv_state_kernel<T>, sgrid, dim3(256), 0, ca, rg));
+    // block-diagonal gates: per block one [2 bs, bs] product, all blocks in one batched launch
+    const void* u_t = kF32 ? (const void*)e->p1 : (const void*)e->t0;
+    CKI(lin(u_t, R, Lr.t[SSDK_HT_RGLRU_GATE].p, bs, e->p2, 2 * R, M, 2 * bs, bs, false, nb, bs, 2LL * bs * bs, 2 * bs));
+    ssdk::RglruArgs a;
+    a.u = e->p1; a.ld_u = R; a.gates = e->p2; a.ld_g = 2 * R; a.gate_bias = Lr.t[SSDK_HT_RGLRU_GATE_B].p; a.lam = Lr.t[SSDK_HT_RGLRU_LAM].p;
+    a.y = e->p0; a.ld_y = 2 * R; a.y_bias = Lr.t[SSDK_HT_RGLRU_IN_B].p; a.out = e->t1; a.S = st; a.slot_stride = e->slot_floats;
+    a.R = R; a.bs = bs; a.decay_mult = c.decay_mult;
+    CKI(L.go(ssdk::rglru_scan_kernel<T>, dim3(rg.n_seqs, (R + 127) / 128), dim3(128), 0, a, rg));
+    return lin(e->t1, R, Lr.t[SSDK_HT_MIX_OUT].p, R, e->mix_out, W, M, W, R);
+  }
+
+  int selective(HybLayer& Lr) {
+    const ssdk_hyb_layer_cfg& c = Lr.c;
+    const int W = e->cfg.width, I = c.inner, N = c.state, Rk = c.dt_rank, taps = c.conv, Nx = Rk + 2 * N;
+    CKI(check_tensor(Lr, SSDK_HT_SEL_IN, 2 * I, W, "mamba.in")); CKI(check_tensor(Lr, SSDK_HT_CONV_W, I, taps, "conv"));
+    CKI(check_tensor(Lr, SSDK_HT_CONV_B, I, 1, "conv.b")); CKI(check_tensor(Lr, SSDK_HT_SEL_X, Nx, I, "mamba.x"));
+    CKI(check_tensor(Lr, SSDK_HT_SEL_DT, I, Rk, "mamba.dt")); CKI(check_tensor(Lr, SSDK_HT_SEL_DT_B, I, 1, "mamba.dt.b"));
+    CKI(check_tensor(Lr, SSDK_HT_SEL_ALOG, I, N, "mamba.A_log")); CKI(check_tensor(Lr, SSDK_HT_SEL_D, I, 1, "mamba.D"));
+    CKI(check_tensor(Lr, SSDK_HT_MIX_OUT, W, I, "mix.o"));
+    CKI(lin(hin, W, Lr.t[SSDK_HT_SEL_IN].p, W, e->p0, 2 * I, M, 2 * I, W));   // x | z
+    float* st = e->state + Lr.state_off;
+    ssdk::ConvArgs ca = {};
+    ca.in = e->p0; ca.ld_in = 2 * I; ca.w = Lr.t[SSDK_HT_CONV_W].p; ca.bias = Lr.t[SSDK_HT_CONV_B].p; ca.out = e->p1; ca.ld_out = I;
+    ca.out_t = kF32 ? nullptr : e->t0; ca.ld_t = I; ca.hist = st + (size_t)I * N; ca.slot_stride = e->slot_floats; ca.C = I; ca.taps = taps;
+    CKI(L.go(ssdk::short_conv_kernel<T, 1>, dim3(M, (I + 255) / 256), dim3(256), 0, ca, rg));
+    CKI(L.go(ssdk::conv_state_kernel<T>, dim3(rg.n_seqs, (I + 255) / 256), dim3(256), 0, ca, rg));
+    const void* x_t = kF32 ? (const void*)e->p1 : (const void*)e->t0;
+    CKI(lin(x_t, I, Lr.t[SSDK_HT_SEL_X].p, I, e->p2, Nx, M, Nx, I));          // dt (low rank) | B | C
+    float* dtz = e->p2 + (size_t)M * Nx;
+    if (kF32) {
+      CKI(lin(e->p2, Nx, Lr.t[SSDK_HT_SEL_DT].p, Rk, dtz, I, M, I, Rk));
+    } else {
+      CKI(L.go(ssdk::cast_cols_kernel<T>, dim3(M), dim3(128), 0, (const float*)e->p2, Nx, (T*)e->t1, Rk, Rk));
+      CKI(lin(e->t1, Rk, Lr.t[SSDK_HT_SEL_DT].p, Rk, dtz, I, M, I, Rk));
+    }
+    ssdk::SelScanArgs a;
+    a.x = e->p1; a.ld_x = I; a.dtz = dtz; a.ld_dt = I; a.dt_bias = Lr.t[SSDK_HT_SEL_DT_B].p; a.bc = e->p2 + Rk; a.ld_bc = Nx;
+    a.A_log = Lr.t[SSDK_HT_SEL_ALOG].p; a.Dw = Lr.t[SSDK_HT_SEL_D].p; a.z = e->p0 + I; a.ld_z = 2 * I; a.out = e->t1;
+    a.S = st; a.slot_stride = e->slot_floats; a.inner = I; a.N = N;
+    const dim3 grid(rg.n_seqs, (I + 127) / 128), block(128);
+    const size_t smem = (size_t)ssdk::kSelRows * 2 * N * 4;
+    if (N <= 16) CKI(L.go(ssdk::selective_scan_kernel<T, 16>, grid, block, smem, a, rg));
+    else if (N <= 32) CKI(L.go(ssdk::selective_scan_kernel<T, 32>, grid, block, smem, a, rg));
+    else if (N <= 64) CKI(L.go(ssdk::selective_scan_kernel<T, 64>, grid, block, smem, a, rg));
+    else CKI(L.go(ssdk::selective_scan_kernel<T, 0>, grid, block, smem, a, rg));
+    return lin(e->t1, I, Lr.t[SSDK_HT_MIX_OUT].p, I, e->mix_out, W, M, W, I);
+  }
+
+  // grouped-query sink attention over the layer's page pool: z holds q | k | v (fp32); og [G, M, H/G, V] fp32
+  int gqa_attention(HybLayer& Lr, const float* z, int ldz, float* og) {
+    const ssdk_hyb_layer_cfg& c = Lr.c;
+    const int H = c.heads, G = c.kv_heads, D = c.dim, V = c.vdim, hpg = H / G;
+    if (!e->cache) return fail("hybrid: attention cache not bound");
+    uint8_t* pool = e->cache + (size_t)e->num_blocks * e->cfg.block_size * Lr.cache_rows_before * e->esz;
+    ssdk::GqaPrepArgs pa;
+    pa.z = z; pa.ldz = ldz; pa.q = e->qcat; pa.cache = pool; pa.inv_freq = c.rot_dims >= 2 ? Lr.inv_freq : nullptr;
+    pa.H = H; pa.G = G; pa.D = D; pa.V = V; pa.rot_dims = c.rot_dims; pa.qk_norm = c.qk_norm; pa.rot_mult = Lr.rot_mult; pa.eps = e->cfg.eps;
+    CKI(L.go(ssdk::gqa_prep_kernel<T>, dim3(M, H + G), dim3(32), 0, pa, rg));
+    bool fused_decode = false;
+    {
+      int n_dec = 0, ctx_max = 0;
+      for (int s = 0; s < rg.n_seqs; ++s)
+        if (h_cu[s + 1] - h_cu[s] == 1) { ++n_dec; ctx_max = std::max(ctx_max, h_pos0[s] + 1); }
+      const int vpl = (V + 31) / 32;
+      if (n_dec > 0 && vpl <= 8 && e->use_decode_attn) {
+        int splits = std::max(1, std::min({32, 2 * num_sms() / std::max(1, n_dec * H), (ctx_max + 127) / 128}));
+        const size_t per_split = (size_t)rg.n_seqs * H * (V + 2);
+        splits = (int)std::min<size_t>(splits, e->att_elems / per_split);
+        if (splits >= 1) {
+          ssdk::GqaDecodeArgs da;
+          da.q = e->qcat; da.cache = pool; da.part = e->att_s; da.out = og; da.H = H; da.G = G; da.D = D; da.V = V; da.splits = splits;
+          da.scale = c.attn_scale; da.sink = c.sink;
+          const dim3 grid(rg.n_seqs, H, splits), block(ssdk::kGqaDecWarps * 32);
+          const size_t smem = ssdk::gqa_decode_smem(D, V);
+          if (vpl <= 1) CKI(L.go(ssdk::gqa_decode_partial_kernel<T, 1>, grid, block, smem, da, rg));
+          else if (vpl <= 2) CKI(L.go(ssdk::gqa_decode_partial_kernel<T, 2>, grid, block, smem, da, rg));
+          else if (vpl <= 4) CKI(L.go(ssdk::gqa_decode_partial_kernel<T, 4>, grid, block, smem, da, rg));
+          else CKI(L.go(ssdk::gqa_decode_partial_kernel<T, 8>, grid, block, smem, da, rg));
+          CKI(L.go(ssdk::gqa_decode_merge_kernel, dim3(rg.n_seqs, H), dim3(64), 0, da, rg));
+          fused_decode = true;
+        }
+      }
+    }
+    for (int s = 0; s < rg.n_seqs; ++s) {
+      const int r0 = h_cu[s], n = h_cu[s + 1] - r0, p0 = h_pos0[s], ctx = p0 + n, ctx_pad = (ctx + 7) / 8 * 8;
+      if (fused_decode && n == 1) continue;
+      CKI(L.go(ssdk::kv_gather_kernel<T>, dim3(ctx_pad), dim3(128), 0, (const T*)pool, (T*)e->keys, (T*)e->lat_t, rg, s, ctx, ctx_pad, G, D, V));
+      const int qb = (int)std::max<size_t>(1, e->att_elems / ((size_t)H * ctx_pad));
+      for (int q0 = 0; q0 < n; q0 += qb) {
+        const int nq = std::min(qb, n - q0), rows = nq * hpg, cb = (p0 + q0 + nq + 7) / 8 * 8;
+        const T* qrows = (const T*)e->qcat + (size_t)(r0 + q0) * hpg * D;
+        CKI(lin(qrows, D, e->keys, D, e->att_s, cb, rows, cb, D, false, G, (long long)M * hpg * D, (long long)ctx_pad * D,
+                (long long)rows * cb, false));
+        CKI(L.go(ssdk::sink_softmax_kernel<T>, dim3(G * rows), dim3(256), 0, (const float*)e->att_s, (T*)e->att_p, (const T*)nullptr, hpg, cb,
+                 p0 + q0, c.attn_scale, rows, c.sink));
+        CKI(lin(e->att_p, cb, e->lat_t, ctx_pad, og + (size_t)(r0 + q0) * hpg * V, V, rows, V, cb, false, G, (long long)rows * cb,
+                (long long)V * ctx_pad, (long long)M * hpg * V, false));
+      }
+    }
+    return 0;
+  }
+
+  int attn_delta(HybLayer& Lr) {
+    const ssdk_hyb_layer_cfg& c = Lr.c;
+    const int W = e->cfg.width, H = c.heads, G = c.kv_heads, D = c.dim, V = c.vdim, taps = c.conv;
+    const int Hd = c.d_heads, Gd = c.d_kv_heads, Dd = c.d_dim, Vd = c.d_vdim;
+    const int HV = H * V, dGD = Gd * Dd, dHV = Hd * Vd, Cd = 2 * dGD + dHV;
+    const int o_g = H * D + G * D + G * V, o_dq = o_g + HV, o_dg = o_dq + Cd, o_b = o_dg + dHV, Ntot = o_b + 2 * Hd;
+    CKI(check_tensor(Lr, SSDK_HT_PAIR_IN, Ntot, W, "pair.in")); CKI(check_tensor(Lr, SSDK_HT_ATTN_OUT, W, HV, "left.o"));
+    CKI(check_tensor(Lr, SSDK_HT_MIX_OUT, W, dHV, "right.o")); CKI(check_tensor(Lr, SSDK_HT_CONV_W, Cd, taps, "right.conv"));
+    CKI(check_tensor(Lr, SSDK_HT_DELTA_ALOG, Hd, 1, "right.A_log")); CKI(check_tensor(Lr, SSDK_HT_DELTA_DT_B, Hd, 1, "right.dt_bias"));
+    CKI(check_tensor(Lr, SSDK_HT_MIX_NORM, dHV, 1, "right.norm"));
+    CKI(lin(hin, W, Lr.t[SSDK_HT_PAIR_IN].p, W, e->p0, Ntot, M, Ntot, W));
+    // left: attention
+    CKI(gqa_attention(Lr, e->p0, Ntot, e->p1));
+    CKI(L.go(ssdk::attn_gate_kernel<T>, dim3(M), dim3(256), 0, (const float*)e->p1, (const float*)(e->p0 + o_g), Ntot, (T*)e->t0, M, H, G, V));
+    CKI(lin(e->t0, HV, Lr.t[SSDK_HT_ATTN_OUT].p, HV, e->mix_out, W, M, W, HV));
+    // right: gated delta rule
+    float* st = e->state + Lr.state_off;
+    ssdk::DeltaPrepArgs dp = {};
+    dp.conv.in = e->p0 + o_dq; dp.conv.ld_in = Ntot; dp.conv.w = Lr.t[SSDK_HT_CONV_W].p; dp.conv.hist = st + (size_t)Hd * Dd * Vd;
+    dp.conv.slot_stride = e->slot_floats; dp.conv.C = Cd; dp.conv.taps = taps;
+    dp.ba = e->p0 + o_b; dp.ld_ba = Ntot; dp.A_log = Lr.t[SSDK_HT_DELTA_ALOG].p; dp.dt_bias = Lr.t[SSDK_HT_DELTA_DT_B].p;
+    dp.q = e->p2; dp.k = dp.q + (size_t)M * dGD; dp.v = dp.k + (size_t)M * dGD; dp.beta = dp.v + (size_t)M * dHV; dp.decay = dp.beta + (size_t)M * Hd;
+    dp.H = Hd; dp.G = Gd; dp.D = Dd; dp.V = Vd; dp.q_scale = 1.0f / sqrtf((float)Dd); dp.unit_eps = 1e-6f;
+    CKI(L.go(ssdk::delta_prep_kernel<T>, dim3(M), dim3(256), (size_t)Cd * 4, dp, rg));
+    CKI(L.go(ssdk::conv_state_kernel<T>, dim3(rg.n_seqs, (Cd + 255) / 256), dim3(256), 0, dp.conv, rg));
+    ssdk::DeltaArgs da;
+    da.q = dp.q; da.k = dp.k; da.v = dp.v; da.beta = dp.beta; da.decay = dp.decay; da.o = e->p1; da.S = st; da.slot_stride = e->slot_floats;
+    da.H = Hd; da.G = Gd; da.D = Dd; da.V = Vd;
+    const int Vr = (Vd + 31) / 32 * 32;
+    const dim3 grid(rg.n_seqs, Hd), block(Vr);
+    if (Dd <= 32) CKI(L.go(ssdk::delta_scan_kernel<T, 32>, grid, block, ssdk::delta_scan_smem(Dd, Vr, 32), da, rg));
+    else if (Dd <= 64) CKI(L.go(ssdk::delta_scan_kernel<T, 64>, grid, block, ssdk::delta_scan_smem(Dd, Vr, 64), da, rg));
+    else if (Dd <= 128) CKI(L.go(ssdk::delta_scan_kernel<T, 128>, grid, block, ssdk::delta_scan_smem(Dd, Vr, 128), da, rg));
+    else CKI(L.go(ssdk::delta_scan_kernel<T, 0>, grid, block, ssdk::delta_scan_smem(Dd, Vr, 0), da, rg));
+    CKI(L.go(ssdk::head_rmsnorm_gate_kernel<T, 0>, dim3(M, Hd), dim3(std::min(256, Vr)), 0, (const float*)e->p1, (const float*)(e->p0 + o_dg), Ntot,
+             (const T*)Lr.t[SSDK_HT_MIX_NORM].p, (T*)e->t1, Hd, Vd, e->cfg.eps));
+    return lin(e->t1, dHV, Lr.t[SSDK_HT_MIX_OUT].p, dHV, e->mix2, W, M, W, dHV);
+  }
+
+  int run_mixer(HybLayer& Lr) {
+    switch (Lr.c.mixer) {
+      case SSDK_MIX_WKV: return wkv(Lr);
+      case SSDK_MIX_MLSTM: return mlstm(Lr);
+      case SSDK_MIX_LATENT_ATTN: return latent(Lr);
+      case SSDK_MIX_RGLRU: return rglru(Lr);
+      case SSDK_MIX_SELECTIVE: return selective(Lr);
+      default: return attn_delta(Lr);
+    }
+  }
+
+  // x += m * norm1(mixer(x)); x += m * norm2(ff(x)): both sublayers read the residual stream itself
+  int serial_layer(HybLayer& Lr) {
+    const ssdk_hyb_cfg& g = e->cfg;
+    const int W = g.width;
+    T* xt = kF32 ? nullptr : (T*)e->h;
+    hin = kF32 ? (const void*)e->x : (const void*)e->h;
+    CKI(check_tensor(Lr, SSDK_HT_NORM, W, 1, "norm1"));
+    if (Lr.c.mixer == SSDK_MIX_WKV || Lr.c.mixer == SSDK_MIX_MLSTM || Lr.c.mixer == SSDK_MIX_LATENT_ATTN)
+      return fail("wkv, mlstm and latent attention are built for parallel blocks");
+    CKI(run_mixer(Lr));
+    const bool pair = Lr.c.mixer == SSDK_MIX_ATTN_DELTA;
+    CKI(L.go(ssdk::postnorm_residual_kernel<T>, dim3(M), dim3(256), 0, e->x, (const float*)e->mix_out, pair ? Lr.c.left_scale : 1.0f,
+             (const float*)(pair ? e->mix2 : nullptr), pair ? Lr.c.right_scale : 0.f, (const T*)Lr.t[SSDK_HT_NORM].p, W, g.eps, g.norm_offset,
+             g.residual_mult, xt));
+    if (Lr.c.mlp == SSDK_MLP_GLU) {
+      CKI(check_tensor(Lr, SSDK_HT_NORM2, W, 1, "norm2"));
+      CKI(glu(Lr));
+      CKI(L.go(ssdk::postnorm_residual_kernel<T>, dim3(M), dim3(256), 0, e->x, (const float*)e->mix_out, 1.0f, (const float*)nullptr, 0.f,
+               (const T*)Lr.t[SSDK_HT_NORM2].p, W, g.eps, g.norm_offset, g.residual_mult, xt));
+    }
+    return 0;
+  }
+
   int layer(HybLayer& Lr, int li) {
+    if (e->cfg.block == SSDK_BLOCK_SERIAL_POSTNORM) return serial_layer(Lr);
     const int W = e->cfg.width;
+    hin = e->h;
     CKI(check_tensor(Lr, SSDK_HT_NORM, W, 1, "norm1")); CKI(check_tensor(Lr, SSDK_HT_LS_MIX, W, 1, "ls1"));
-    CKI(L.go(ssdk::unit_offset_rmsnorm_kernel<T>, dim3(M), dim3(256), 0, (const float*)e->x, (const T*)Lr.t[SSDK_HT_NORM].p, (T*)e->h,
-             (const int*)nullptr, W, e->cfg.eps));
-    if (Lr.c.mixer == SSDK_MIX_WKV) CKI(wkv(Lr));
-    else if (Lr.c.mixer == SSDK_MIX_MLSTM) CKI(mlstm(Lr));
-    else CKI(latent(Lr));
+    CKI(L.go(ssdk::offset_rmsnorm_kernel<T>, dim3(M), dim3(256), 0, (const float*)e->x, (const T*)Lr.t[SSDK_HT_NORM].p, (T*)e->h,
+             (const int*)nullptr, W, e->cfg.eps, e->cfg.norm_offset));
+    if (Lr.c.mixer == SSDK_MIX_ATTN_DELTA) return fail("the attention pair is built for serial blocks");
+    CKI(run_mixer(Lr));
     ssdk::CombineArgs ca = {};
     ca.x = e->x; ca.mix = e->mix_out; ca.ls1 = Lr.t[SSDK_HT_LS_MIX].p; ca.width = W;
     if (Lr.c.mlp == SSDK_MLP_MOE) {
@@ -475,6 +718,13 @@ static int hyb_smem_attrs(ssdk_hyb_engine* e) {
 #undef SSDK_SCAN_ATTR
   CK(cudaFuncSetAttribute(ssdk::latent_decode_partial_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   CK(cudaFuncSetAttribute(ssdk::latent_decode_partial_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+#define SSDK_DELTA_ATTR(DR) \
+  CK(cudaFuncSetAttribute(ssdk::delta_scan_kernel<bf16, DR>, cudaFuncAttributeMaxDynamicSharedMemorySize, big)); \
+  CK(cudaFuncSetAttribute(ssdk::delta_scan_kernel<float, DR>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+  SSDK_DELTA_ATTR(0) SSDK_DELTA_ATTR(32) SSDK_DELTA_ATTR(64) SSDK_DELTA_ATTR(128)
+#undef SSDK_DELTA_ATTR
+  CK(cudaFuncSetAttribute(ssdk::delta_prep_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+  CK(cudaFuncSetAttribute(ssdk::delta_prep_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   e->smem_attr_done = true;
   return 0;
 }
@@ -505,15 +755,16 @@ static int hyb_forward_t(ssdk_hyb_engine* e, int n_seqs, int M, const int32_t* i
   run.e = e; run.L.st = st; run.L.pdl = false; run.M = M; run.h_cu = cu; run.h_pos0 = pos0;
   run.rg.cu = d + o_cu; run.rg.pos0 = d + o_pos; run.rg.slot = d + o_slot; run.rg.tok_seq = d + o_seq; run.rg.tables = d + o_tab;
   run.rg.n_seqs = n_seqs; run.rg.M = M; run.rg.max_blocks = g.max_blocks_per_seq; run.rg.block_size = g.block_size;
-  CKI(run.L.go(ssdk::embed_rows_kernel<T>, dim3(M), dim3(128), 0, (const int*)(d + o_ids), (const T*)e->embed.p, e->x, g.width, g.vocab));
+  CKI(run.L.go(ssdk::embed_rows_kernel<T>, dim3(M), dim3(128), 0, (const int*)(d + o_ids), (const T*)e->embed.p, e->x, g.width, g.vocab,
+               g.embed_scale, (g.block == SSDK_BLOCK_SERIAL_POSTNORM && !std::is_same<T, float>::value) ? (T*)e->h : (T*)nullptr));
   for (int li = 0; li < g.n_layers; ++li) {
     CKI(run.layer(e->layers[li], li));
     if (residual_host)
       CK(cudaMemcpyAsync(residual_host + (size_t)li * M * g.width, e->x, (size_t)M * g.width * 4, cudaMemcpyDeviceToHost, st));
   }
   if (n_want > 0) {
-    CKI(run.L.go(ssdk::unit_offset_rmsnorm_kernel<T>, dim3(n_want), dim3(256), 0, (const float*)e->x, (const T*)e->final_norm.p, (T*)e->hn,
-                 (const int*)(d + o_want), g.width, g.eps));
+    CKI(run.L.go(ssdk::offset_rmsnorm_kernel<T>, dim3(n_want), dim3(256), 0, (const float*)e->x, (const T*)e->final_norm.p, (T*)e->hn,
+                 (const int*)(d + o_want), g.width, g.eps, g.norm_offset));
     CKI(run.lin(e->hn, g.width, e->head.p, g.width, e->logits, g.vocab, n_want, g.vocab, g.width));
     if (logits_host) CK(cudaMemcpyAsync(logits_host, e->logits, (size_t)n_want * g.vocab * 4, cudaMemcpyDeviceToHost, st));
     if (temps && out_tokens) {
@@ -545,6 +796,7 @@ int ssdk_hyb_create(const ssdk_hyb_cfg* cfg, const ssdk_hyb_layer_cfg* layers, s
   if (!cfg || !layers || !out) return fail("ssdk_hyb_create: null argument");
   if (cfg->width < 1 || cfg->vocab < 1 || cfg->n_layers < 1) return fail("ssdk_hyb_create: bad sizes");
   if (cfg->dtype != SSDK_DT_F32 && cfg->dtype != SSDK_DT_BF16) return fail("ssdk_hyb_create: unknown dtype %d", cfg->dtype);
+  if (cfg->block != SSDK_BLOCK_PARALLEL_PRENORM && cfg->block != SSDK_BLOCK_SERIAL_POSTNORM) return fail("ssdk_hyb_create: unknown block kind %d", cfg->block);
   if (cfg->max_tokens < 1 || cfg->max_seqs < 1 || cfg->max_logit_rows < 1 || cfg->block_size < 1 || cfg->max_blocks_per_seq < 1)
     return fail("ssdk_hyb_create: bad runtime limits");
   int ndev = 0;
@@ -558,10 +810,24 @@ int ssdk_hyb_create(const ssdk_hyb_cfg* cfg, const ssdk_hyb_layer_cfg* layers, s
   for (int i = 0; i < cfg->n_layers; ++i) e->layers[i].c = layers[i];
   if (hyb_derive(e) != 0) { delete e; return -1; }
   for (auto& L : e->layers) {
-    if (L.c.mixer != SSDK_MIX_LATENT_ATTN || L.c.rot_dims < 2) continue;
+    if ((L.c.mixer != SSDK_MIX_LATENT_ATTN && L.c.mixer != SSDK_MIX_ATTN_DELTA) || L.c.rot_dims < 2) continue;
     const int half = L.c.rot_dims / 2;
     std::vector<float> f(half);
-    for (int i = 0; i < half; ++i) f[i] = (float)pow((double)L.c.rot_base, -2.0 * i / (double)L.c.rot_dims);
+    const double dims = (double)L.c.rot_dims, base = (double)L.c.rot_base;
+    for (int i = 0; i < half; ++i) f[i] = (float)pow(base, -2.0 * i / dims);
+    if (L.c.mixer == SSDK_MIX_ATTN_DELTA && L.c.yarn_factor > 0.f) {
+      // YaRN: dimensions that turn fewer than `slow` times over the original length are slowed by `factor`, those that
+      // turn more than `fast` times are kept, a linear ramp in between; cos and sin grow by 0.1 ln(factor) + 1
+      const double kPi = 3.14159265358979323846, factor = (double)L.c.yarn_factor, orig = (double)L.c.yarn_original;
+      auto dim_of = [&](double turns) { return dims * log(orig / (2.0 * kPi * turns)) / (2.0 * log(base)); };
+      const double lo = std::max(floor(dim_of((double)L.c.yarn_fast)), 0.0), hi = std::min(ceil(dim_of((double)L.c.yarn_slow)), dims - 1.0);
+      for (int i = 0; i < half; ++i) {
+        const double fi = pow(base, -2.0 * i / dims);
+        const double ramp = std::min(std::max(((double)i - lo) / std::max(hi - lo, 0.001), 0.0), 1.0);
+        f[i] = (float)(fi / factor * ramp + fi * (1.0 - ramp));
+      }
+      L.rot_mult = (float)(0.1 * log(factor) + 1.0);
+    }
     if (cudaMalloc(&L.inv_freq, half * 4) != cudaSuccess ||
         cudaMemcpy(L.inv_freq, f.data(), half * 4, cudaMemcpyHostToDevice) != cudaSuccess) {
       delete e;
@@ -612,7 +878,7 @@ int64_t ssdk_hyb_workspace_bytes(ssdk_hyb_handle e) { return e ? e->ws_bytes : -
 int ssdk_hyb_bind_pools(ssdk_hyb_handle e, void* cache, int64_t num_blocks, void* state, int64_t n_slots, void* workspace,
                         int64_t workspace_bytes) {
   if (!e) return fail("ssdk_hyb_bind_pools: null handle");
-  if (e->cache_row_total && (!cache || num_blocks < 1)) return fail("ssdk_hyb_bind_pools: the model has latent attention but no cache was given");
+  if (e->cache_row_total && (!cache || num_blocks < 1)) return fail("ssdk_hyb_bind_pools: the model has attention layers but no cache was given");
   if (e->slot_floats && (!state || n_slots < 1)) return fail("ssdk_hyb_bind_pools: the model has recurrent layers but no state pool was given");
   if (!workspace || workspace_bytes < e->ws_bytes) return fail("ssdk_hyb_bind_pools: workspace too small");
   if (((uintptr_t)workspace & 255) || ((uintptr_t)cache & 15) || ((uintptr_t)state & 15)) return fail("ssdk_hyb_bind_pools: misaligned pool");

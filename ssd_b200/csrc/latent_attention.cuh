@@ -111,16 +111,20 @@ __global__ void latent_gather_kernel(const T* __restrict__ cache, T* __restrict_
   }
 }
 
-// Softmax with a sink over the score rows of one query block.  Row r = (query q0 + r / H, head r % H); the query at
-// position pos sees keys 0 .. pos.  sc [rows, ld] fp32 raw dot products -> pr [rows, ld] (T) weights, zero beyond pos and
-// in the padding.  The sink logit joins the maximum and adds exp(sink - max) to the denominator; it is not scaled.
+// Softmax with a sink over the score rows of one query block.  The rows come in `batches` of rows_per_batch (one batch
+// per key/value head of grouped-query attention; a single batch for latent attention); inside a batch row r is
+// (query q0 + r / H, head r % H) with H the heads that share the batch's keys, and the query at position pos sees keys
+// 0 .. pos.  sc [rows, ld] fp32 raw dot products -> pr [rows, ld] (T) weights, zero beyond pos and in the padding.
+// The sink is a learned per-head logit (`sink`, indexed batch * H + head) or, without one, the constant sink_const added
+// to the denominator (0: plain softmax); it joins the maximum, is not scaled and contributes nothing to the output.
 template <typename T>
 __global__ void sink_softmax_kernel(const float* __restrict__ sc, T* __restrict__ pr, const T* __restrict__ sink, int H, int ld,
-                                    int pos_first, float scale) {
+                                    int pos_first, float scale, int rows_per_batch, float sink_const) {
   __shared__ float red[33];
-  const int r = blockIdx.x, h = r % H, n = pos_first + r / H + 1;  // keys this row sees
+  const int r = blockIdx.x, batch = r / rows_per_batch, rb = r - batch * rows_per_batch;
+  const int h = rb % H, n = pos_first + rb / H + 1;  // keys this row sees
   const float* srow = sc + (size_t)r * ld;
-  const float sk = ld_f<T>(sink + h);
+  const float sk = sink ? ld_f<T>(sink + batch * H + h) : (sink_const > 0.f ? logf(sink_const) : -INFINITY);
   float mx = sk;
   for (int j = threadIdx.x; j < n; j += blockDim.x) mx = fmaxf(mx, srow[j] * scale);
   __syncthreads();

@@ -1,7 +1,9 @@
 // layer_ops.cuh — the element-wise steps of a layered (hybrid) model's block.  The residual stream, every norm
 // statistic and every gate are fp32; T (bf16 or float) is the storage type of the activations that feed a linear layer.
-//   embed_rows_kernel         x = embed[token]                                  (fp32 residual)
-//   unit_offset_rmsnorm_kernel y = x / sqrt(mean(x^2) + eps) * (1 + w)           (unit-offset weight: the scale is 1 + w)
+//   embed_rows_kernel         x = embed[token] * scale                          (fp32 residual; optional T copy)
+//   offset_rmsnorm_kernel     y = x / sqrt(mean(x^2) + eps) * (offset + w)       (offset 1: unit-offset weight, 0: plain)
+//   postnorm_residual_kernel  x += mult * norm(s1 y1 + s2 y2): the norm sits on a sublayer's OUTPUT (serial blocks)
+//   glu_act_kernel            y = gelu_tanh(g) * u
 //   token_shift_kernel        RWKV token shift: S mixes h + (h_prev - h) * mu_s, h_prev carried in the state slot
 //   head_rmsnorm_gate_kernel  per-head unit RMS, times a channel weight, times silu / sigmoid of a gate pre-activation
 //   clamped_glu_kernel        y = g * sigmoid(1.702 g) * (u + 1) with g = min(g, lim), u = clamp(u, -lim, lim)
@@ -25,17 +27,21 @@ struct Ragged {
 
 template <typename T>
 __global__ void embed_rows_kernel(const int* __restrict__ ids, const T* __restrict__ embed, float* __restrict__ x, int width,
-                                  int vocab) {
+                                  int vocab, float scale, T* __restrict__ xt) {
   const int m = blockIdx.x;
   int id = ids[m];
   id = min(max(id, 0), vocab - 1);
-  for (int c = threadIdx.x; c < width; c += blockDim.x) x[(size_t)m * width + c] = ld_f<T>(embed + (size_t)id * width + c);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = ld_f<T>(embed + (size_t)id * width + c) * scale;
+    x[(size_t)m * width + c] = v;
+    if (xt) st_f<T>(xt + (size_t)m * width + c, v);
+  }
 }
 
 // rows: optional gather (row r of the output reads x[rows[r]])
 template <typename T>
-__global__ void unit_offset_rmsnorm_kernel(const float* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
-                                           const int* __restrict__ rows, int width, float eps) {
+__global__ void offset_rmsnorm_kernel(const float* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
+                                      const int* __restrict__ rows, int width, float eps, float offset) {
   __shared__ float red[33];
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * width;
@@ -44,7 +50,41 @@ __global__ void unit_offset_rmsnorm_kernel(const float* __restrict__ x, const T*
   ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)width + eps);
   for (int c = threadIdx.x; c < width; c += blockDim.x)
-    st_f<T>(y + (size_t)r * width + c, xr[c] * inv * (1.0f + ld_f<T>(w + c)));
+    st_f<T>(y + (size_t)r * width + c, xr[c] * inv * (offset + ld_f<T>(w + c)));
+}
+
+// Serial post-norm block: x[m] += mult * (y / sqrt(mean(y^2) + eps)) * (offset + w) with y = s1 y1[m] (+ s2 y2[m]); the
+// updated row is also written in the storage type (xt, may be null) for the next sublayer's projections.
+template <typename T>
+__global__ void postnorm_residual_kernel(float* __restrict__ x, const float* __restrict__ y1, float s1, const float* __restrict__ y2,
+                                         float s2, const T* __restrict__ w, int width, float eps, float offset, float mult,
+                                         T* __restrict__ xt) {
+  __shared__ float red[33];
+  const size_t base = (size_t)blockIdx.x * width;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = y2 ? fmaf(s2, y2[base + c], s1 * y1[base + c]) : s1 * y1[base + c];
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = y2 ? fmaf(s2, y2[base + c], s1 * y1[base + c]) : s1 * y1[base + c];
+    const float xn = fmaf(mult, v * inv * (offset + ld_f<T>(w + c)), x[base + c]);
+    x[base + c] = xn;
+    if (xt) st_f<T>(xt + base + c, xn);
+  }
+}
+
+// z [rows, ldz] fp32 with gate columns [0, ff) and up columns [ff, 2 ff) -> y [rows, ff] (T) = gelu_tanh(gate) * up
+template <typename T>
+__global__ void glu_act_kernel(const float* __restrict__ z, int ldz, T* __restrict__ y, int ff) {
+  const int r = blockIdx.x;
+  for (int c = threadIdx.x; c < ff; c += blockDim.x) {
+    const float g = z[(size_t)r * ldz + c];
+    const float a = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    st_f<T>(y + (size_t)r * ff + c, a * z[(size_t)r * ldz + ff + c]);
+  }
 }
 
 // mixes[s][m][c] = h[m][c] + (prev[m][c] - h[m][c]) * mu[s][c]; prev of a portion's first row comes from the slot

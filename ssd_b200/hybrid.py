@@ -1,6 +1,12 @@
-"""Layered ("hybrid") models: a program of layers, each one token mixer + an optional mixture-of-experts feed-forward
-in a parallel block.  The design served through this module is Pikavik (config.json `"architecture": "Pikavik"`): mLSTM,
-RWKV-style wkv and latent-attention mixers in any order.
+"""Layered ("hybrid") models: a program of layers, each one token mixer + an optional feed-forward.  Two designs are
+served through this module, told apart by config.json's `"architecture"`:
+
+    Pikavik   parallel pre-norm blocks (mixer and mixture-of-experts feed-forward read the same normed input, unit-offset
+              norm weights, layer scales); mixers mLSTM, RWKV-style wkv and latent attention
+    Kefurax   serial post-norm blocks (x += m * norm(sublayer(x)): the sublayers read x itself, plain norm weights, scaled
+              embedding); mixers rglru (gated diagonal recurrence behind a short convolution), mamba1 (selective scan)
+              and `parallel` (grouped-query sink attention with YaRN-scaled interleaved rotation beside a gated delta
+              rule); dense gelu-GLU feed-forward
 
     HybridSpec     what config.json (and, for sizes it does not list, the checkpoint's tensor shapes) says
     load_hybrid_weights   safetensors -> device tensors in the packed layout libssdk's ssdk_hyb_bind expects
@@ -22,7 +28,16 @@ import torch
 
 from . import lib as L
 
-MIXERS = {"wkv": L.MIX_WKV, "mlstm": L.MIX_MLSTM, "latent_attention": L.MIX_LATENT_ATTN}
+MIXERS = {"wkv": L.MIX_WKV, "mlstm": L.MIX_MLSTM, "latent_attention": L.MIX_LATENT_ATTN, "rglru": L.MIX_RGLRU,
+          "mamba1": L.MIX_SELECTIVE, "parallel": L.MIX_ATTN_DELTA}
+# which mixers and feed-forwards a design may list, and how its blocks join the residual stream
+DESIGNS = {
+    "Pikavik": {"mixers": ("wkv", "mlstm", "latent_attention"), "mlp": ("moe",), "block": L.BLOCK_PARALLEL_PRENORM,
+                "norm_offset": 1.0},
+    "Kefurax": {"mixers": ("rglru", "mamba1", "parallel"), "mlp": ("dense",), "block": L.BLOCK_SERIAL_POSTNORM,
+                "norm_offset": 0.0},
+}
+RGLRU_DECAY_MULT = 8.0  # log a = -8 r softplus(lam)
 
 
 @dataclass
@@ -50,12 +65,38 @@ class LayerSpec:
     limit: float = 0.0
     shared_ff: int = 0
     shared_limit: float = 0.0
+    # grouped-query attention of the `parallel` mixer (heads / dim / vdim / rot_dims / rot_base / attn_scale above)
+    kv_heads: int = 0
+    qk_norm: int = 0
+    sink: float = 0.0
+    yarn_factor: float = 0.0
+    yarn_original: float = 0.0
+    yarn_fast: float = 0.0
+    yarn_slow: float = 0.0
+    # short convolution; rglru (inner channels, blocks); selective scan (inner, state, dt_rank)
+    conv: int = 0
+    inner: int = 0
+    blocks: int = 0
+    state: int = 0
+    dt_rank: int = 0
+    decay_mult: float = 0.0
+    # gated delta rule of the `parallel` mixer
+    d_heads: int = 0
+    d_kv_heads: int = 0
+    d_dim: int = 0
+    d_vdim: int = 0
+    left_scale: float = 1.0
+    right_scale: float = 1.0
 
     def cfg(self) -> L.HybLayerCfg:
+        mlp = {"moe": L.MLP_MOE, "dense": L.MLP_GLU, None: L.MLP_NONE}[self.mlp]
         return L.HybLayerCfg(MIXERS[self.mixer], self.heads, self.dim, self.vdim, self.rot_dim, self.rot_dims, self.kv_rank,
                              self.q_rank, self.decay_rank, self.rot_base, self.attn_scale, self.gate_cap,
-                             L.MLP_MOE if self.mlp == "moe" else L.MLP_NONE, self.experts, self.top, self.groups, self.keep,
-                             self.ff, self.shared_ff, self.route_scale, self.limit, self.shared_limit)
+                             mlp, self.experts, self.top, self.groups, self.keep,
+                             self.ff, self.shared_ff, self.route_scale, self.limit, self.shared_limit,
+                             self.kv_heads, self.qk_norm, self.sink, self.yarn_factor, self.yarn_original, self.yarn_fast,
+                             self.yarn_slow, self.conv, self.inner, self.blocks, self.state, self.dt_rank, self.decay_mult,
+                             self.d_heads, self.d_kv_heads, self.d_dim, self.d_vdim, self.left_scale, self.right_scale)
 
 
 @dataclass
@@ -65,10 +106,23 @@ class HybridSpec:
     eps: float
     layers: list[LayerSpec] = field(default_factory=list)
     architecture: str = "Pikavik"
+    embed_scale: float = 1.0
+    residual_mult: float = 1.0
 
     @property
-    def has_latent(self) -> bool:
-        return any(l.mixer == "latent_attention" for l in self.layers)
+    def block(self) -> int:
+        return DESIGNS[self.architecture]["block"]
+
+    @property
+    def norm_offset(self) -> float:
+        return DESIGNS[self.architecture]["norm_offset"]
+
+    @property
+    def has_cache(self) -> bool:
+        """Some layer keeps per-token rows in the paged cache (latent or grouped-query attention)."""
+        return any(l.mixer in ("latent_attention", "parallel") for l in self.layers)
+
+    has_latent = has_cache
 
     @property
     def has_state(self) -> bool:
@@ -78,12 +132,35 @@ class HybridSpec:
     def from_config(cls, cfg: dict, shapes: dict[str, list[int]] | None = None) -> "HybridSpec":
         """cfg: the parsed config.json.  shapes: tensor name -> shape of the checkpoint, for the sizes that only a
         tensor gives (the rank of the wkv decay bottleneck)."""
+        arch = cfg.get("architecture", "Pikavik")
+        if arch not in DESIGNS:
+            raise ValueError(f"unknown layered design {arch!r}")
+        design = DESIGNS[arch]
         layers = []
         for i, lc in enumerate(cfg["layers"]):
             kind, m = lc["type"], lc["mixer"]
-            if kind not in MIXERS:
-                raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
-            ls = LayerSpec(mixer=kind, heads=int(m["heads"]), dim=int(m["dim"]))
+            if kind not in design["mixers"]:
+                raise ValueError(f"layer {i}: {arch} has no mixer type {kind!r}")
+            if kind == "rglru":
+                ls = LayerSpec(mixer=kind, heads=1, dim=1, inner=int(m["width"]), blocks=int(m["blocks"]), conv=int(m["conv"]),
+                               decay_mult=RGLRU_DECAY_MULT)
+            elif kind == "mamba1":
+                ls = LayerSpec(mixer=kind, heads=1, dim=1, inner=int(m["inner"]), state=int(m["state"]),
+                               dt_rank=int(m["dt_rank"]), conv=int(m["conv"]))
+            elif kind == "parallel":
+                a, d = m["left"], m["right"]
+                rot = a.get("rot") or {}
+                sc = rot.get("scaling") or {}
+                ls = LayerSpec(mixer=kind, heads=int(a["heads"]), kv_heads=int(a["kv_heads"]), dim=int(a["dim"]),
+                               vdim=int(a["vdim"]), attn_scale=float(a["scale"]), qk_norm=1, sink=1.0,
+                               rot_dims=int(rot.get("dims", 0)), rot_base=float(rot.get("base", 10000.0)),
+                               yarn_factor=float(sc.get("factor", 0.0)), yarn_original=float(sc.get("original", 0.0)),
+                               yarn_fast=float(sc.get("fast", 0.0)), yarn_slow=float(sc.get("slow", 0.0)),
+                               d_heads=int(d["heads"]), d_kv_heads=int(d["kv_heads"]), d_dim=int(d["dim"]),
+                               d_vdim=int(d["vdim"]), conv=int(d["conv"]), left_scale=float(m["left_scale"]),
+                               right_scale=float(m["right_scale"]))
+            else:
+                ls = LayerSpec(mixer=kind, heads=int(m["heads"]), dim=int(m["dim"]))
             if kind == "wkv":
                 ls.vdim = ls.dim
                 if shapes is not None:
@@ -94,25 +171,30 @@ class HybridSpec:
                     raise ValueError(f"layer {i}: the decay bottleneck's rank is unknown")
             elif kind == "mlstm":
                 ls.vdim, ls.gate_cap = int(m["vdim"]), float(m["gate_cap"])
-            else:
+            elif kind == "latent_attention":
                 rot = m.get("rot") or {}
                 ls.vdim, ls.rot_dim = int(m["vdim"]), int(m["rot_dim"])
                 ls.rot_dims, ls.rot_base = int(rot.get("dims", ls.rot_dim)), float(rot.get("base", 10000.0))
                 ls.kv_rank, ls.q_rank, ls.attn_scale = int(m["kv_rank"]), int(m["q_rank"]), float(m["scale"])
             mlp = lc.get("mlp")
             if mlp:
-                if mlp.get("kind", "moe") != "moe":
-                    raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
-                r, ex, sh = mlp["router"], mlp["expert"], mlp.get("shared")
-                g = r.get("groups") or {}
-                ls.mlp, ls.experts, ls.top = "moe", int(r["experts"]), int(r["top"])
-                ls.groups, ls.keep = int(g.get("count", 1)), int(g.get("keep", g.get("count", 1)))
-                ls.route_scale, ls.ff, ls.limit = float(r.get("scale", 1.0)), int(ex["ff"]), float(ex["limit"])
-                if sh:
-                    ls.shared_ff, ls.shared_limit = int(sh["ff"]), float(sh["limit"])
+                mk = mlp.get("kind", design["mlp"][0])
+                if mk not in design["mlp"]:
+                    raise ValueError(f"layer {i}: unknown feed-forward kind {mk!r}")
+                if mk == "dense":
+                    ls.mlp, ls.ff = "dense", int(mlp["ff"])
+                else:
+                    r, ex, sh = mlp["router"], mlp["expert"], mlp.get("shared")
+                    g = r.get("groups") or {}
+                    ls.mlp, ls.experts, ls.top = "moe", int(r["experts"]), int(r["top"])
+                    ls.groups, ls.keep = int(g.get("count", 1)), int(g.get("keep", g.get("count", 1)))
+                    ls.route_scale, ls.ff, ls.limit = float(r.get("scale", 1.0)), int(ex["ff"]), float(ex["limit"])
+                    if sh:
+                        ls.shared_ff, ls.shared_limit = int(sh["ff"]), float(sh["limit"])
             layers.append(ls)
         return cls(width=int(cfg["width"]), vocab=int(cfg["vocab"]), eps=float(cfg["norm"]["eps"]), layers=layers,
-                   architecture=cfg.get("architecture", "Pikavik"))
+                   architecture=arch, embed_scale=float((cfg.get("embedding") or {}).get("scale", 1.0)),
+                   residual_mult=float(cfg.get("residual_mult", 1.0)))
 
     @classmethod
     def from_dir(cls, path: str) -> "HybridSpec":
@@ -162,8 +244,29 @@ def pack_hybrid_weights(spec: HybridSpec, raw: dict[str, torch.Tensor], dtype: t
     w = {"EMBED": dev(t("embed")), "HEAD": dev(t("head")), "FINAL_NORM": dev(t("final.norm")), "layers": []}
     for i, ls in enumerate(spec.layers):
         p, mx = f"l{i}.", f"l{i}.mix."
-        lw = {"NORM": dev(t(p + "norm1")), "LS_MIX": dev(t(p + "ls1")), "MIX_OUT": dev(t(mx + "o"))}
-        if ls.mixer == "wkv":
+        lw = {"NORM": dev(t(p + "norm1"))}
+        if ls.mixer in ("wkv", "mlstm", "latent_attention"):
+            lw["LS_MIX"], lw["MIX_OUT"] = dev(t(p + "ls1")), dev(t(mx + "o"))
+        if ls.mixer == "rglru":
+            lw["RGLRU_IN"] = dev(torch.cat([t(mx + "y"), t(mx + "x")]))
+            lw["RGLRU_IN_B"] = dev(torch.cat([t(mx + "y.b"), t(mx + "x.b")]))
+            lw["CONV_W"], lw["CONV_B"] = dev(t(mx + "conv")), dev(t(mx + "conv.b"))
+            lw["RGLRU_GATE"] = dev(torch.cat([t(mx + "ra"), t(mx + "ri")], dim=1))      # [blocks, 2 bs, bs]
+            lw["RGLRU_GATE_B"] = dev(torch.cat([t(mx + "ra.b"), t(mx + "ri.b")], dim=1))  # [blocks, 2 bs]
+            lw["RGLRU_LAM"], lw["MIX_OUT"] = dev(t(mx + "lam")), dev(t(mx + "o"))
+        elif ls.mixer == "mamba1":
+            lw["SEL_IN"], lw["CONV_W"], lw["CONV_B"] = dev(t(mx + "in")), dev(t(mx + "conv")), dev(t(mx + "conv.b"))
+            lw["SEL_X"], lw["SEL_DT"], lw["SEL_DT_B"] = dev(t(mx + "x")), dev(t(mx + "dt")), dev(t(mx + "dt.b"))
+            lw["SEL_ALOG"], lw["SEL_D"], lw["MIX_OUT"] = dev(t(mx + "A_log")), dev(t(mx + "D")), dev(t(mx + "o"))
+        elif ls.mixer == "parallel":
+            a, d = mx + "left.", mx + "right."
+            lw["PAIR_IN"] = dev(torch.cat([t(a + "q"), t(a + "k"), t(a + "v"), t(a + "g"),
+                                           t(d + "q"), t(d + "k"), t(d + "v"), t(d + "g"), t(d + "b"), t(d + "a")]))
+            lw["ATTN_OUT"], lw["MIX_OUT"] = dev(t(a + "o")), dev(t(d + "o"))
+            lw["CONV_W"] = dev(torch.cat([t(d + "q.conv"), t(d + "k.conv"), t(d + "v.conv")]))
+            lw["DELTA_ALOG"], lw["DELTA_DT_B"] = dev(t(d + "A_log")), dev(t(d + "dt_bias"))
+            lw["MIX_NORM"] = dev(t(d + "norm").repeat(ls.d_heads))  # one weight per value channel, the same for every head
+        elif ls.mixer == "wkv":
             lw["WKV_MU"] = dev(torch.stack([t(mx + "mu." + s) for s in "rkvgw"]))
             for s in "rkvg":
                 lw["WKV_" + s.upper()] = dev(t(mx + s))
@@ -177,6 +280,10 @@ def pack_hybrid_weights(spec: HybridSpec, raw: dict[str, torch.Tensor], dtype: t
             lw["LAT_QNORM"], lw["LAT_KVNORM"] = dev(t(mx + "dq.norm")), dev(t(mx + "dkv.norm"))
             lw["LAT_UQ"], lw["LAT_UV"], lw["LAT_SINK"] = dev(t(mx + "uq")), dev(t(mx + "uv")), dev(t(mx + "sink"))
             lw["LAT_UKT"] = dev(t(mx + "uk").view(ls.heads, ls.dim, ls.kv_rank).transpose(1, 2))
+        if ls.mlp == "dense":
+            q = p + "mlp."
+            lw["NORM2"] = dev(t(p + "norm2"))
+            lw["GLU_IN"], lw["GLU_OUT"] = dev(torch.cat([t(q + "gate"), t(q + "up")])), dev(t(q + "down"))
         if ls.mlp == "moe":
             q = p + "mlp."
             lw["LS_MLP"], lw["ROUTER"] = dev(t(p + "ls2")), dev(t(q + "router"))
@@ -261,7 +368,8 @@ class HybridRunner:
         # logits of one call live on the device as fp32 + bf16: all rows of a call unless that exceeds ~6 GB
         self.max_logit_rows = max_logit_rows or max(1, min(max_tokens, (1 << 30) // spec.vocab))
         cfg = L.HybCfg(spec.width, spec.vocab, len(spec.layers), L.DT_BF16 if self.dtype == torch.bfloat16 else L.DT_F32,
-                       spec.eps, max_tokens, max_seqs, self.max_logit_rows, block_size, self.max_blocks, 0)
+                       spec.eps, max_tokens, max_seqs, self.max_logit_rows, block_size, self.max_blocks, spec.block, spec.norm_offset,
+                       spec.embed_scale, spec.residual_mult)
         layer_cfgs = (L.HybLayerCfg * len(spec.layers))(*[l.cfg() for l in spec.layers])
         h = C.c_void_p()
         L.check(self.lib.ssdk_hyb_create(C.byref(cfg), layer_cfgs, C.byref(h)), "ssdk_hyb_create")

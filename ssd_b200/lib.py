@@ -48,6 +48,12 @@ class HybLayerCfg(C.Structure):
         ("mlp", C.c_int32), ("experts", C.c_int32), ("top", C.c_int32), ("groups", C.c_int32), ("keep", C.c_int32),
         ("ff", C.c_int32), ("shared_ff", C.c_int32), ("route_scale", C.c_float), ("limit", C.c_float),
         ("shared_limit", C.c_float),
+        ("kv_heads", C.c_int32), ("qk_norm", C.c_int32), ("sink", C.c_float), ("yarn_factor", C.c_float),
+        ("yarn_original", C.c_float), ("yarn_fast", C.c_float), ("yarn_slow", C.c_float),
+        ("conv", C.c_int32), ("inner", C.c_int32), ("blocks", C.c_int32), ("state", C.c_int32), ("dt_rank", C.c_int32),
+        ("decay_mult", C.c_float),
+        ("d_heads", C.c_int32), ("d_kv_heads", C.c_int32), ("d_dim", C.c_int32), ("d_vdim", C.c_int32),
+        ("left_scale", C.c_float), ("right_scale", C.c_float),
     ]
 
 
@@ -57,17 +63,20 @@ class HybCfg(C.Structure):
     _fields_ = [
         ("width", C.c_int32), ("vocab", C.c_int32), ("n_layers", C.c_int32), ("dtype", C.c_int32), ("eps", C.c_float),
         ("max_tokens", C.c_int32), ("max_seqs", C.c_int32), ("max_logit_rows", C.c_int32), ("block_size", C.c_int32),
-        ("max_blocks_per_seq", C.c_int32), ("reserved", C.c_int32),
+        ("max_blocks_per_seq", C.c_int32), ("block", C.c_int32), ("norm_offset", C.c_float), ("embed_scale", C.c_float),
+        ("residual_mult", C.c_float),
     ]
 
 
 # hybrid-model enums (include/ssdk.h)
 DT_F32, DT_BF16 = 0, 1
-MIX_WKV, MIX_MLSTM, MIX_LATENT_ATTN = 0, 1, 2
-MLP_NONE, MLP_MOE = 0, 1
+MIX_WKV, MIX_MLSTM, MIX_LATENT_ATTN, MIX_RGLRU, MIX_SELECTIVE, MIX_ATTN_DELTA = 0, 1, 2, 3, 4, 5
+MLP_NONE, MLP_MOE, MLP_GLU = 0, 1, 2
+BLOCK_PARALLEL_PRENORM, BLOCK_SERIAL_POSTNORM = 0, 1
 HT_NAMES = ("EMBED HEAD FINAL_NORM NORM LS_MIX LS_MLP WKV_MU WKV_R WKV_K WKV_V WKV_G WKV_W1 WKV_W2 WKV_W0 WKV_U MLSTM_IN "
             "MLSTM_IB MLSTM_FB LAT_DOWN LAT_QNORM LAT_KVNORM LAT_UQ LAT_UKT LAT_UV LAT_SINK MIX_NORM MIX_OUT ROUTER "
-            "EXPERT_IN EXPERT_OUT SHARED_IN SHARED_OUT").split()
+            "EXPERT_IN EXPERT_OUT SHARED_IN SHARED_OUT NORM2 GLU_IN GLU_OUT CONV_W CONV_B RGLRU_IN RGLRU_IN_B RGLRU_GATE "
+            "RGLRU_GATE_B RGLRU_LAM SEL_IN SEL_X SEL_DT SEL_DT_B SEL_ALOG SEL_D PAIR_IN ATTN_OUT DELTA_ALOG DELTA_DT_B").split()
 HT = {n: i for i, n in enumerate(HT_NAMES)}
 
 # weight kinds (enum in include/ssdk.h)
