@@ -263,29 +263,35 @@ struct DeltaArgs {
 
 constexpr int kDeltaRows = 8;  // rows staged together
 
-inline size_t delta_scan_smem(int D, int Vr, int DR) {
-  const int DP = DR > 0 ? DR : D;
-  return ((size_t)(DR > 0 ? 0 : D * Vr) + (size_t)kDeltaRows * (2 * DP + Vr + 2)) * 4;
+// shared memory of delta_scan_kernel<DR> with G row groups (DR == 0: G = 1 and the state itself lives there)
+inline size_t delta_scan_smem(int D, int Vr, int DR, int G) {
+  const int DP = DR > 0 ? DR * G : D;
+  return ((size_t)(DR > 0 ? 0 : D * Vr) + (size_t)kDeltaRows * (2 * DP + Vr + 2) + (size_t)2 * G * Vr) * 4;
 }
 
-// grid (n_seqs, H), blockDim = V rounded up to a warp: thread j owns column j of the head's D x V state, so both
-// contractions over D (S^T k and S^T q) are thread-local sums in row order and the walk needs no reduction across
-// threads.  DR > 0: the column lives in registers (D <= DR, padded rows meet k = q = 0); DR == 0: in shared memory.
-template <typename T, int DR>
+// grid (n_seqs, H), block (Vr, G) with Vr = V rounded up to a warp: thread (j, gi) owns rows [gi DR, (gi + 1) DR) of
+// column j of the head's D x V state, in registers.  Both contractions over D (S^T k and S^T q) are thread-local sums over
+// the thread's rows; with G > 1 the row groups' partial sums meet in shared memory and are added in group order (two
+// CTA barriers per row, none with G == 1).  Padded rows meet k = q = 0.  DR == 0: any D, one group, the column lives in
+// shared memory.  Everything is fp32 whatever the model's storage type.
+template <int DR>
 __global__ void delta_scan_kernel(const DeltaArgs p, const Ragged rg) {
   extern __shared__ float ds_sm[];
-  const int s = blockIdx.x, hd = blockIdx.y, g = hd / (p.H / p.G), j = threadIdx.x, Vr = blockDim.x;
-  const int D = p.D, V = p.V, DP = DR > 0 ? DR : D;
+  const int s = blockIdx.x, hd = blockIdx.y, g = hd / (p.H / p.G);
+  const int j = threadIdx.x, gi = threadIdx.y, Vr = blockDim.x, NG = blockDim.y, tid = gi * Vr + j, nthr = Vr * NG;
+  const int D = p.D, V = p.V, DP = DR > 0 ? DR * NG : D;
   float* Ssm = ds_sm;                                     // [D][Vr] (DR == 0)
   float* kq = ds_sm + (DR > 0 ? 0 : (size_t)D * Vr);      // [rows][2 DP]: k then q
   float* vs = kq + kDeltaRows * 2 * DP;                   // [rows][Vr]
   float* bg = vs + kDeltaRows * Vr;                       // [rows][2]: beta, decay
+  float* part = bg + kDeltaRows * 2;                      // [2][NG][Vr] partial contractions
   float Sr[DR > 0 ? DR : 1];
   const bool col = j < V, carried = rg.pos0[s] > 0;
+  const int d0 = gi * DR;
   float* Sg = p.S + (size_t)rg.slot[s] * p.slot_stride + (size_t)hd * D * V + (col ? j : 0);
   if (DR > 0) {
 #pragma unroll
-    for (int d = 0; d < DR; ++d) Sr[d] = (col && carried && d < D) ? Sg[(size_t)d * V] : 0.f;
+    for (int d = 0; d < DR; ++d) Sr[d] = (col && carried && d0 + d < D) ? Sg[(size_t)(d0 + d) * V] : 0.f;
   } else {
     for (int d = 0; d < D; ++d) Ssm[(size_t)d * Vr + j] = (col && carried) ? Sg[(size_t)d * V] : 0.f;
   }
@@ -293,29 +299,60 @@ __global__ void delta_scan_kernel(const DeltaArgs p, const Ragged rg) {
   for (int m0 = r0; m0 < r1; m0 += kDeltaRows) {
     const int nr = min(kDeltaRows, r1 - m0);
     __syncthreads();
-    for (int i = j; i < nr * DP; i += Vr) {
+    for (int i = tid; i < nr * DP; i += nthr) {
       const int r = i / DP, d = i - r * DP;
       kq[r * 2 * DP + d] = d < D ? p.k[(size_t)(m0 + r) * GD + g * D + d] : 0.f;
       kq[r * 2 * DP + DP + d] = d < D ? p.q[(size_t)(m0 + r) * GD + g * D + d] : 0.f;
     }
-    for (int r = 0; r < nr; ++r) vs[r * Vr + j] = col ? p.v[(size_t)(m0 + r) * HV + hd * V + j] : 0.f;
-    if (j < nr) {
-      bg[2 * j] = p.beta[(size_t)(m0 + j) * p.H + hd];
-      bg[2 * j + 1] = p.decay[(size_t)(m0 + j) * p.H + hd];
+    for (int i = tid; i < nr * Vr; i += nthr) {
+      const int r = i / Vr, c = i - r * Vr;
+      vs[i] = c < V ? p.v[(size_t)(m0 + r) * HV + hd * V + c] : 0.f;
+    }
+    if (tid < nr) {
+      bg[2 * tid] = p.beta[(size_t)(m0 + tid) * p.H + hd];
+      bg[2 * tid + 1] = p.decay[(size_t)(m0 + tid) * p.H + hd];
     }
     __syncthreads();
     for (int r = 0; r < nr; ++r) {
-      const float* kr = kq + r * 2 * DP;
+      const float* kr = kq + r * 2 * DP + d0;
       const float* qr = kr + DP;
       const float beta = bg[2 * r], dec = bg[2 * r + 1];
-      float dot = 0.f, o = 0.f;
+      float o = 0.f;
       if (DR > 0) {
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-        for (int d = 0; d < DR; ++d) { Sr[d] *= dec; dot = fmaf(Sr[d], kr[d], dot); }
+        for (int d = 0; d < DR; d += 4) {
+          Sr[d] *= dec; Sr[d + 1] *= dec; Sr[d + 2] *= dec; Sr[d + 3] *= dec;
+          a0 = fmaf(Sr[d], kr[d], a0); a1 = fmaf(Sr[d + 1], kr[d + 1], a1);
+          a2 = fmaf(Sr[d + 2], kr[d + 2], a2); a3 = fmaf(Sr[d + 3], kr[d + 3], a3);
+        }
+        float dot = (a0 + a1) + (a2 + a3);
+        if (NG > 1) {
+          part[gi * Vr + j] = dot;
+          __syncthreads();
+          dot = part[j];
+          for (int w = 1; w < NG; ++w) dot += part[w * Vr + j];
+        }
         const float u = beta * (vs[r * Vr + j] - dot);
+        a0 = a1 = a2 = a3 = 0.f;
 #pragma unroll
-        for (int d = 0; d < DR; ++d) { Sr[d] = fmaf(kr[d], u, Sr[d]); o = fmaf(Sr[d], qr[d], o); }
+        for (int d = 0; d < DR; d += 4) {
+          Sr[d] = fmaf(kr[d], u, Sr[d]); Sr[d + 1] = fmaf(kr[d + 1], u, Sr[d + 1]);
+          Sr[d + 2] = fmaf(kr[d + 2], u, Sr[d + 2]); Sr[d + 3] = fmaf(kr[d + 3], u, Sr[d + 3]);
+          a0 = fmaf(Sr[d], qr[d], a0); a1 = fmaf(Sr[d + 1], qr[d + 1], a1);
+          a2 = fmaf(Sr[d + 2], qr[d + 2], a2); a3 = fmaf(Sr[d + 3], qr[d + 3], a3);
+        }
+        o = (a0 + a1) + (a2 + a3);
+        if (NG > 1) {
+          part[(NG + gi) * Vr + j] = o;
+          __syncthreads();
+          if (gi == 0) {
+            o = part[NG * Vr + j];
+            for (int w = 1; w < NG; ++w) o += part[(NG + w) * Vr + j];
+          }
+        }
       } else {
+        float dot = 0.f;
         for (int d = 0; d < D; ++d) {
           const float sv = Ssm[(size_t)d * Vr + j] * dec;
           Ssm[(size_t)d * Vr + j] = sv;
@@ -328,14 +365,14 @@ __global__ void delta_scan_kernel(const DeltaArgs p, const Ragged rg) {
           o = fmaf(sv, qr[d], o);
         }
       }
-      if (col) p.o[(size_t)(m0 + r) * HV + hd * V + j] = o;
+      if (col && gi == 0) p.o[(size_t)(m0 + r) * HV + hd * V + j] = o;
     }
   }
   if (col) {
     if (DR > 0) {
 #pragma unroll
       for (int d = 0; d < DR; ++d)
-        if (d < D) Sg[(size_t)d * V] = Sr[d];
+        if (d0 + d < D) Sg[(size_t)(d0 + d) * V] = Sr[d];
     } else {
       for (int d = 0; d < D; ++d) Sg[(size_t)d * V] = Ssm[(size_t)d * Vr + j];
     }

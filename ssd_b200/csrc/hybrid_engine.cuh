@@ -71,6 +71,16 @@ struct ssdk_hyb_engine {
   bool smem_attr_done = false;
 };
 
+// delta rule: rows of a state column per thread (DR) and row groups (NG); DR = 0: the shared-memory walk
+static void delta_shape(int D, int Vr, int* DR, int* NG) {
+  *DR = 0; *NG = 1;
+  if (D <= 16) { *DR = 16; return; }
+  for (int dr : {32, 64}) {
+    const int g = (D + dr - 1) / dr;
+    if (Vr * g <= 512 && g <= 8) { *DR = dr; *NG = g; return; }  // 512 threads: the register file holds DR + ~40 each
+  }
+}
+
 static int hyb_derive(ssdk_hyb_engine* e) {
   const ssdk_hyb_cfg& g = e->cfg;
   size_t soff = 0, crow = 0;
@@ -116,7 +126,12 @@ static int hyb_derive(ssdk_hyb_engine* e) {
       if (V > 256 * 4) return fail("attention: value size %d too large", V);
       if (Hd < 1 || Gd < 1 || Hd % Gd || Dd < 1 || Vd < 1 || Vd > 1024 || c.conv < 1)
         return fail("delta rule: %d heads on %d query/key heads, %d x %d, %d taps", Hd, Gd, Dd, Vd, c.conv);
-      if (Dd > 128 && ssdk::delta_scan_smem(Dd, (Vd + 31) / 32 * 32, 0) > 200 * 1024) return fail("delta rule: head %d x %d too large", Dd, Vd);
+      {
+        const int Vr = (Vd + 31) / 32 * 32;
+        int dr = 0, ng = 1;
+        delta_shape(Dd, Vr, &dr, &ng);
+        if (dr == 0 && ssdk::delta_scan_smem(Dd, Vr, 0, 1) > 200 * 1024) return fail("delta rule: head %d x %d too large", Dd, Vd);
+      }
       const long long Cd = 2LL * Gd * Dd + (long long)Hd * Vd;
       soff += (size_t)Hd * Dd * Vd + (size_t)(c.conv - 1) * Cd;
       L.cache_row = (size_t)G * (D + V);
@@ -637,11 +652,14 @@ struct HybRun {
     da.q = dp.q; da.k = dp.k; da.v = dp.v; da.beta = dp.beta; da.decay = dp.decay; da.o = e->p1; da.S = st; da.slot_stride = e->slot_floats;
     da.H = Hd; da.G = Gd; da.D = Dd; da.V = Vd;
     const int Vr = (Vd + 31) / 32 * 32;
-    const dim3 grid(rg.n_seqs, Hd), block(Vr);
-    if (Dd <= 32) CKI(L.go(ssdk::delta_scan_kernel<T, 32>, grid, block, ssdk::delta_scan_smem(Dd, Vr, 32), da, rg));
-    else if (Dd <= 64) CKI(L.go(ssdk::delta_scan_kernel<T, 64>, grid, block, ssdk::delta_scan_smem(Dd, Vr, 64), da, rg));
-    else if (Dd <= 128) CKI(L.go(ssdk::delta_scan_kernel<T, 128>, grid, block, ssdk::delta_scan_smem(Dd, Vr, 128), da, rg));
-    else CKI(L.go(ssdk::delta_scan_kernel<T, 0>, grid, block, ssdk::delta_scan_smem(Dd, Vr, 0), da, rg));
+    int DR = 0, NG = 1;
+    delta_shape(Dd, Vr, &DR, &NG);
+    const dim3 grid(rg.n_seqs, Hd), block(Vr, NG);
+    const size_t smem = ssdk::delta_scan_smem(Dd, Vr, DR, NG);
+    if (DR == 16) CKI(L.go(ssdk::delta_scan_kernel<16>, grid, block, smem, da, rg));
+    else if (DR == 32) CKI(L.go(ssdk::delta_scan_kernel<32>, grid, block, smem, da, rg));
+    else if (DR == 64) CKI(L.go(ssdk::delta_scan_kernel<64>, grid, block, smem, da, rg));
+    else CKI(L.go(ssdk::delta_scan_kernel<0>, grid, block, smem, da, rg));
     CKI(L.go(ssdk::head_rmsnorm_gate_kernel<T, 0>, dim3(M, Hd), dim3(std::min(256, Vr)), 0, (const float*)e->p1, (const float*)(e->p0 + o_dg), Ntot,
              (const T*)Lr.t[SSDK_HT_MIX_NORM].p, (T*)e->t1, Hd, Vd, e->cfg.eps));
     return lin(e->t1, dHV, Lr.t[SSDK_HT_MIX_OUT].p, dHV, e->mix2, W, M, W, dHV);
@@ -718,11 +736,10 @@ static int hyb_smem_attrs(ssdk_hyb_engine* e) {
 #undef SSDK_SCAN_ATTR
   CK(cudaFuncSetAttribute(ssdk::latent_decode_partial_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   CK(cudaFuncSetAttribute(ssdk::latent_decode_partial_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-#define SSDK_DELTA_ATTR(DR) \
-  CK(cudaFuncSetAttribute(ssdk::delta_scan_kernel<bf16, DR>, cudaFuncAttributeMaxDynamicSharedMemorySize, big)); \
-  CK(cudaFuncSetAttribute(ssdk::delta_scan_kernel<float, DR>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-  SSDK_DELTA_ATTR(0) SSDK_DELTA_ATTR(32) SSDK_DELTA_ATTR(64) SSDK_DELTA_ATTR(128)
-#undef SSDK_DELTA_ATTR
+  CK(cudaFuncSetAttribute(ssdk::delta_scan_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+  CK(cudaFuncSetAttribute(ssdk::delta_scan_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+  CK(cudaFuncSetAttribute(ssdk::delta_scan_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+  CK(cudaFuncSetAttribute(ssdk::delta_scan_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   CK(cudaFuncSetAttribute(ssdk::delta_prep_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   CK(cudaFuncSetAttribute(ssdk::delta_prep_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
   e->smem_attr_done = true;

@@ -113,9 +113,10 @@ def rotate_interleaved(v, pos, rot):
     return out
 
 
-def sink_attention(h, W, p, mx, eps, state, p0):
+def sink_attention(h, W, p, mx, eps, state, p0, sink=1.0):
     """Grouped-query causal softmax attention whose denominator has one extra 1 (a sink of score 0 without a value),
-    rotary positions, unit-RMS queries and keys, and a sigmoid output gate."""
+    rotary positions, unit-RMS queries and keys, and a sigmoid output gate.  (`sink` is the design's 1; the tests pass 0
+    to show that a plain softmax would give other numbers.)"""
     n = h.shape[0]
     H, G, D, V = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
     pos = list(range(p0, p0 + n))
@@ -137,7 +138,7 @@ def sink_attention(h, W, p, mx, eps, state, p0):
             s = (K[:ctx, g] @ q[t, hd]) * mx["scale"]
             m = max(s.max().item(), 0.0)
             e = torch.exp(s - m)
-            out[t, hd] = (e[:, None] * Vc[:ctx, g]).sum(0) / (math.exp(-m) + e.sum())
+            out[t, hd] = (e[:, None] * Vc[:ctx, g]).sum(0) / (sink * math.exp(-m) + e.sum())
     gate = torch.sigmoid(h @ W[p + ".g"].T)
     return (out.reshape(n, H * V) * gate) @ W[p + ".o"].T
 
