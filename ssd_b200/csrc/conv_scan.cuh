@@ -105,7 +105,11 @@ struct RglruArgs {
   float decay_mult;
 };
 
-// grid (n_seqs, ceil(R / blockDim)): one thread per channel walks its sequence's rows
+constexpr int kRglruRows = 8;  // rows whose inputs are requested together
+
+// grid (n_seqs, ceil(R / blockDim)): one thread per channel walks its sequence's rows.  Rows are taken eight at a time:
+// their loads are issued together and everything that does not depend on the state (both gates, the decay, the input's
+// weight, the gelu branch) is evaluated for the eight rows side by side; only S = a S + b runs in sequence.
 template <typename T>
 __global__ void rglru_scan_kernel(const RglruArgs p, const Ragged rg) {
   const int s = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -118,14 +122,30 @@ __global__ void rglru_scan_kernel(const RglruArgs p, const Ragged rg) {
   float* Sp = p.S + (size_t)rg.slot[s] * p.slot_stride + c;
   float S = rg.pos0[s] > 0 ? *Sp : 0.f;
   const int r0 = rg.cu[s], r1 = rg.cu[s + 1];
-  for (int m = r0; m < r1; ++m) {
-    const float r = sigmoid_f(p.gates[(size_t)m * p.ld_g + gr] + rb);
-    const float i = sigmoid_f(p.gates[(size_t)m * p.ld_g + gi] + ib);
-    const float log_a = -r * sp;
-    const float a = expf(log_a);
-    // 1 - a^2 through expm1: exact also where a is within an ulp of 1
-    S = fmaf(a, S, sqrtf(-expm1f(2.0f * log_a)) * i * p.u[(size_t)m * p.ld_u + c]);
-    st_f<T>((T*)p.out + (size_t)m * p.R + c, S * gelu_tanh_f(p.y[(size_t)m * p.ld_y + c] + yb));
+  for (int m0 = r0; m0 < r1; m0 += kRglruRows) {
+    float zr[kRglruRows], zi[kRglruRows], u[kRglruRows], y[kRglruRows];
+#pragma unroll
+    for (int k = 0; k < kRglruRows; ++k) {
+      const int m = min(m0 + k, r1 - 1);
+      zr[k] = p.gates[(size_t)m * p.ld_g + gr]; zi[k] = p.gates[(size_t)m * p.ld_g + gi];
+      u[k] = p.u[(size_t)m * p.ld_u + c]; y[k] = p.y[(size_t)m * p.ld_y + c];
+    }
+    float a[kRglruRows], bb[kRglruRows];
+#pragma unroll
+    for (int k = 0; k < kRglruRows; ++k) {
+      const float log_a = -sigmoid_f(zr[k] + rb) * sp;
+      a[k] = expf(log_a);
+      // 1 - a^2 through expm1: exact also where a is within an ulp of 1
+      bb[k] = sqrtf(-expm1f(2.0f * log_a)) * sigmoid_f(zi[k] + ib) * u[k];
+      y[k] = gelu_tanh_f(y[k] + yb);
+    }
+#pragma unroll
+    for (int k = 0; k < kRglruRows; ++k) {
+      if (m0 + k < r1) {
+        S = fmaf(a[k], S, bb[k]);
+        st_f<T>((T*)p.out + (size_t)(m0 + k) * p.R + c, S * y[k]);
+      }
+    }
   }
   *Sp = S;
 }
@@ -144,69 +164,87 @@ struct SelScanArgs {
   int inner, N;
 };
 
-constexpr int kSelRows = 8;  // rows whose B | C are staged together
+constexpr int kSelRows = 8;  // rows whose inputs are requested (and whose B | C are staged) together
 
-// grid (n_seqs, ceil(inner / blockDim)).  NT > 0: the channel's N <= NT states live in registers; NT == 0: any N, the
-// state stays in its slot (global memory).  dynamic shared memory: kSelRows * 2 N floats.
+// A channel's N states are spread over LPC = blockDim.x lanes of a warp (a power of two), NT states per lane in
+// registers (N <= NT * LPC); blockDim.y channels per CTA, grid (n_seqs, ceil(inner / blockDim.y)).  Per row a lane
+// advances its states and the lanes' parts of y = sum_n S[n] C[n] meet by shuffle (a fixed tree).  exp(dt A) is taken as
+// exp2(dt (A log2 e)).  NT == 0: any N, one lane per channel, the state stays in its slot (global memory).
+// dynamic shared memory: kSelRows * 2 N floats.
 template <typename T, int NT>
 __global__ void selective_scan_kernel(const SelScanArgs p, const Ragged rg) {
   extern __shared__ float sel_sm[];
-  const int s = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x, N = p.N;
+  const int s = blockIdx.x, lpc = blockDim.x, ln = threadIdx.x, N = p.N;
+  const int c = blockIdx.y * blockDim.y + threadIdx.y, tid = threadIdx.y * lpc + ln, nthr = lpc * blockDim.y;
   const bool live = c < p.inner;
   const bool carried = rg.pos0[s] > 0;
-  float A[NT > 0 ? NT : 1], S[NT > 0 ? NT : 1];
+  const int n0 = ln * NT;  // first state of this lane
+  float A2[NT > 0 ? NT : 1], S[NT > 0 ? NT : 1];
   float* Sg = p.S + (size_t)rg.slot[s] * p.slot_stride + (size_t)(live ? c : 0) * N;
   if (NT > 0) {
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
-      A[n] = (live && n < N) ? -expf(ld_f<T>((const T*)p.A_log + (size_t)c * N + n)) : 0.f;
-      S[n] = (live && n < N && carried) ? Sg[n] : 0.f;
+      const bool ok = live && n0 + n < N;
+      A2[n] = ok ? -expf(ld_f<T>((const T*)p.A_log + (size_t)c * N + n0 + n)) * 1.4426950408889634f : 0.f;
+      S[n] = (ok && carried) ? Sg[n0 + n] : 0.f;
     }
   } else if (live && !carried) {
     for (int n = 0; n < N; ++n) Sg[n] = 0.f;
   }
   const float dtb = live ? ld_f<T>((const T*)p.dt_bias + c) : 0.f, Dc = live ? ld_f<T>((const T*)p.Dw + c) : 0.f;
-  const int r0 = rg.cu[s], r1 = rg.cu[s + 1];
+  const int r0 = rg.cu[s], r1 = rg.cu[s + 1], cc = live ? c : 0;
   for (int m0 = r0; m0 < r1; m0 += kSelRows) {
     const int nr = min(kSelRows, r1 - m0);
+    float dt[kSelRows], xv[kSelRows], zv[kSelRows];
+#pragma unroll
+    for (int r = 0; r < kSelRows; ++r) {
+      const int m = min(m0 + r, r1 - 1);
+      dt[r] = p.dtz[(size_t)m * p.ld_dt + cc]; xv[r] = p.x[(size_t)m * p.ld_x + cc]; zv[r] = p.z[(size_t)m * p.ld_z + cc];
+    }
     __syncthreads();
-    for (int i = threadIdx.x; i < nr * 2 * N; i += blockDim.x) {
+    for (int i = tid; i < nr * 2 * N; i += nthr) {
       const int r = i / (2 * N), k = i - r * 2 * N;
       sel_sm[i] = p.bc[(size_t)(m0 + r) * p.ld_bc + k];
     }
     __syncthreads();
-    if (!live) continue;
-    for (int r = 0; r < nr; ++r) {
-      const int m = m0 + r;
-      const float dt = softplus_f(p.dtz[(size_t)m * p.ld_dt + c] + dtb);
-      const float xv = p.x[(size_t)m * p.ld_x + c], dx = dt * xv;
-      const float* B = sel_sm + r * 2 * N;
-      const float* Cm = B + N;
-      float y = 0.f;
-      if (NT > 0) {
 #pragma unroll
-        for (int n = 0; n < NT; ++n) {
-          if (n < N) {
-            S[n] = fmaf(expf(dt * A[n]), S[n], dx * B[n]);
-            y = fmaf(S[n], Cm[n], y);
+    for (int r = 0; r < kSelRows; ++r) {
+      dt[r] = softplus_f(dt[r] + dtb);
+      zv[r] = silu_f(zv[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < kSelRows; ++r) {
+      if (r < nr) {
+        const int m = m0 + r;
+        const float dx = dt[r] * xv[r];
+        const float* B = sel_sm + r * 2 * N;
+        const float* Cm = B + N;
+        float y = 0.f;
+        if (NT > 0) {
+#pragma unroll
+          for (int n = 0; n < NT; ++n) {
+            if (n0 + n < N) {
+              S[n] = fmaf(exp2f(dt[r] * A2[n]), S[n], dx * B[n0 + n]);
+              y = fmaf(S[n], Cm[n0 + n], y);
+            }
+          }
+          for (int o = lpc >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+        } else if (live) {
+          for (int n = 0; n < N; ++n) {
+            const float a = -expf(ld_f<T>((const T*)p.A_log + (size_t)c * N + n));
+            const float sn = fmaf(expf(dt[r] * a), Sg[n], dx * B[n]);
+            Sg[n] = sn;
+            y = fmaf(sn, Cm[n], y);
           }
         }
-      } else {
-        for (int n = 0; n < N; ++n) {
-          const float a = -expf(ld_f<T>((const T*)p.A_log + (size_t)c * N + n));
-          const float sn = fmaf(expf(dt * a), Sg[n], dx * B[n]);
-          Sg[n] = sn;
-          y = fmaf(sn, Cm[n], y);
-        }
+        if (live && ln == 0) st_f<T>((T*)p.out + (size_t)m * p.inner + c, fmaf(Dc, xv[r], y) * zv[r]);
       }
-      y = fmaf(Dc, xv, y);
-      st_f<T>((T*)p.out + (size_t)m * p.inner + c, y * silu_f(p.z[(size_t)m * p.ld_z + c]));
     }
   }
   if (NT > 0 && live) {
 #pragma unroll
     for (int n = 0; n < NT; ++n)
-      if (n < N) Sg[n] = S[n];
+      if (n0 + n < N) Sg[n0 + n] = S[n];
   }
 }
 
@@ -269,16 +307,18 @@ inline size_t delta_scan_smem(int D, int Vr, int DR, int G) {
   return ((size_t)(DR > 0 ? 0 : D * Vr) + (size_t)kDeltaRows * (2 * DP + Vr + 2) + (size_t)2 * G * Vr) * 4;
 }
 
-// grid (n_seqs, H), block (Vr, G) with Vr = V rounded up to a warp: thread (j, gi) owns rows [gi DR, (gi + 1) DR) of
-// column j of the head's D x V state, in registers.  Both contractions over D (S^T k and S^T q) are thread-local sums over
+// grid (n_seqs, H, column splits), block (Vr, G) with Vr a multiple of 32 columns per CTA (the columns of the state are
+// independent of one another, so a head may be spread over several CTAs): thread (j, gi) owns rows [gi DR, (gi + 1) DR)
+// of one column of the head's D x V state, in registers; k and q are read from shared memory four rows at a time.  Both contractions over D (S^T k and S^T q) are thread-local sums over
 // the thread's rows; with G > 1 the row groups' partial sums meet in shared memory and are added in group order (two
 // CTA barriers per row, none with G == 1).  Padded rows meet k = q = 0.  DR == 0: any D, one group, the column lives in
 // shared memory.  Everything is fp32 whatever the model's storage type.
 template <int DR>
 __global__ void delta_scan_kernel(const DeltaArgs p, const Ragged rg) {
-  extern __shared__ float ds_sm[];
+  extern __shared__ __align__(16) float ds_sm[];
   const int s = blockIdx.x, hd = blockIdx.y, g = hd / (p.H / p.G);
-  const int j = threadIdx.x, gi = threadIdx.y, Vr = blockDim.x, NG = blockDim.y, tid = gi * Vr + j, nthr = Vr * NG;
+  const int jl = threadIdx.x, gi = threadIdx.y, Vr = blockDim.x, NG = blockDim.y, tid = gi * Vr + jl, nthr = Vr * NG;
+  const int j = blockIdx.z * Vr + jl;  // column of the head's state
   const int D = p.D, V = p.V, DP = DR > 0 ? DR * NG : D;
   float* Ssm = ds_sm;                                     // [D][Vr] (DR == 0)
   float* kq = ds_sm + (DR > 0 ? 0 : (size_t)D * Vr);      // [rows][2 DP]: k then q
@@ -293,7 +333,7 @@ __global__ void delta_scan_kernel(const DeltaArgs p, const Ragged rg) {
 #pragma unroll
     for (int d = 0; d < DR; ++d) Sr[d] = (col && carried && d0 + d < D) ? Sg[(size_t)(d0 + d) * V] : 0.f;
   } else {
-    for (int d = 0; d < D; ++d) Ssm[(size_t)d * Vr + j] = (col && carried) ? Sg[(size_t)d * V] : 0.f;
+    for (int d = 0; d < D; ++d) Ssm[(size_t)d * Vr + jl] = (col && carried) ? Sg[(size_t)d * V] : 0.f;
   }
   const int r0 = rg.cu[s], r1 = rg.cu[s + 1], GD = p.G * D, HV = p.H * V;
   for (int m0 = r0; m0 < r1; m0 += kDeltaRows) {
@@ -306,7 +346,8 @@ __global__ void delta_scan_kernel(const DeltaArgs p, const Ragged rg) {
     }
     for (int i = tid; i < nr * Vr; i += nthr) {
       const int r = i / Vr, c = i - r * Vr;
-      vs[i] = c < V ? p.v[(size_t)(m0 + r) * HV + hd * V + c] : 0.f;
+      const int cg = blockIdx.z * Vr + c;
+      vs[i] = cg < V ? p.v[(size_t)(m0 + r) * HV + hd * V + cg] : 0.f;
     }
     if (tid < nr) {
       bg[2 * tid] = p.beta[(size_t)(m0 + tid) * p.H + hd];
@@ -322,46 +363,49 @@ __global__ void delta_scan_kernel(const DeltaArgs p, const Ragged rg) {
         float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
         for (int d = 0; d < DR; d += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(kr + d);
           Sr[d] *= dec; Sr[d + 1] *= dec; Sr[d + 2] *= dec; Sr[d + 3] *= dec;
-          a0 = fmaf(Sr[d], kr[d], a0); a1 = fmaf(Sr[d + 1], kr[d + 1], a1);
-          a2 = fmaf(Sr[d + 2], kr[d + 2], a2); a3 = fmaf(Sr[d + 3], kr[d + 3], a3);
+          a0 = fmaf(Sr[d], k4.x, a0); a1 = fmaf(Sr[d + 1], k4.y, a1);
+          a2 = fmaf(Sr[d + 2], k4.z, a2); a3 = fmaf(Sr[d + 3], k4.w, a3);
         }
         float dot = (a0 + a1) + (a2 + a3);
         if (NG > 1) {
-          part[gi * Vr + j] = dot;
+          part[gi * Vr + jl] = dot;
           __syncthreads();
-          dot = part[j];
-          for (int w = 1; w < NG; ++w) dot += part[w * Vr + j];
+          dot = part[jl];
+          for (int w = 1; w < NG; ++w) dot += part[w * Vr + jl];
         }
-        const float u = beta * (vs[r * Vr + j] - dot);
+        const float u = beta * (vs[r * Vr + jl] - dot);
         a0 = a1 = a2 = a3 = 0.f;
 #pragma unroll
         for (int d = 0; d < DR; d += 4) {
-          Sr[d] = fmaf(kr[d], u, Sr[d]); Sr[d + 1] = fmaf(kr[d + 1], u, Sr[d + 1]);
-          Sr[d + 2] = fmaf(kr[d + 2], u, Sr[d + 2]); Sr[d + 3] = fmaf(kr[d + 3], u, Sr[d + 3]);
-          a0 = fmaf(Sr[d], qr[d], a0); a1 = fmaf(Sr[d + 1], qr[d + 1], a1);
-          a2 = fmaf(Sr[d + 2], qr[d + 2], a2); a3 = fmaf(Sr[d + 3], qr[d + 3], a3);
+          const float4 k4 = *reinterpret_cast<const float4*>(kr + d);
+          const float4 q4 = *reinterpret_cast<const float4*>(qr + d);
+          Sr[d] = fmaf(k4.x, u, Sr[d]); Sr[d + 1] = fmaf(k4.y, u, Sr[d + 1]);
+          Sr[d + 2] = fmaf(k4.z, u, Sr[d + 2]); Sr[d + 3] = fmaf(k4.w, u, Sr[d + 3]);
+          a0 = fmaf(Sr[d], q4.x, a0); a1 = fmaf(Sr[d + 1], q4.y, a1);
+          a2 = fmaf(Sr[d + 2], q4.z, a2); a3 = fmaf(Sr[d + 3], q4.w, a3);
         }
         o = (a0 + a1) + (a2 + a3);
         if (NG > 1) {
-          part[(NG + gi) * Vr + j] = o;
+          part[(NG + gi) * Vr + jl] = o;
           __syncthreads();
           if (gi == 0) {
-            o = part[NG * Vr + j];
-            for (int w = 1; w < NG; ++w) o += part[(NG + w) * Vr + j];
+            o = part[NG * Vr + jl];
+            for (int w = 1; w < NG; ++w) o += part[(NG + w) * Vr + jl];
           }
         }
       } else {
         float dot = 0.f;
         for (int d = 0; d < D; ++d) {
-          const float sv = Ssm[(size_t)d * Vr + j] * dec;
-          Ssm[(size_t)d * Vr + j] = sv;
+          const float sv = Ssm[(size_t)d * Vr + jl] * dec;
+          Ssm[(size_t)d * Vr + jl] = sv;
           dot = fmaf(sv, kr[d], dot);
         }
-        const float u = beta * (vs[r * Vr + j] - dot);
+        const float u = beta * (vs[r * Vr + jl] - dot);
         for (int d = 0; d < D; ++d) {
-          const float sv = fmaf(kr[d], u, Ssm[(size_t)d * Vr + j]);
-          Ssm[(size_t)d * Vr + j] = sv;
+          const float sv = fmaf(kr[d], u, Ssm[(size_t)d * Vr + jl]);
+          Ssm[(size_t)d * Vr + jl] = sv;
           o = fmaf(sv, qr[d], o);
         }
       }
@@ -374,7 +418,7 @@ __global__ void delta_scan_kernel(const DeltaArgs p, const Ragged rg) {
       for (int d = 0; d < DR; ++d)
         if (d0 + d < D) Sg[(size_t)(d0 + d) * V] = Sr[d];
     } else {
-      for (int d = 0; d < D; ++d) Sg[(size_t)d * V] = Ssm[(size_t)d * Vr + j];
+      for (int d = 0; d < D; ++d) Sg[(size_t)d * V] = Ssm[(size_t)d * Vr + jl];
     }
   }
 }

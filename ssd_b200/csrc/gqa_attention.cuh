@@ -92,30 +92,69 @@ struct GqaDecodeArgs {
 
 constexpr int kGqaDecWarps = 4;
 
-inline size_t gqa_decode_smem(int D, int V) { return ((size_t)D + (size_t)kGqaDecWarps * (V + 2)) * 4; }
+inline size_t gqa_decode_smem(int D, int V) { return ((size_t)(D + 3) / 4 * 4 + (size_t)kGqaDecWarps * (V + 2)) * 4; }
+
+// N contiguous elements of storage type T -> floats, with the widest loads their size allows (the caller guarantees that
+// p is aligned to min(16, N * sizeof(T)) bytes)
+template <typename T, int N>
+SSDK_DEVINL void ld_contig(const T* p, float* f) {
+  constexpr int kBytes = N * (int)sizeof(T);
+  if constexpr (kBytes % 16 == 0) {
+    uint32_t w[kBytes / 4];
+#pragma unroll
+    for (int i = 0; i < kBytes / 16; ++i) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(p) + i);
+      w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+    }
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      if constexpr (sizeof(T) == 4) f[i] = __uint_as_float(w[i]);
+      else f[i] = __uint_as_float((i & 1) ? (w[i >> 1] & 0xffff0000u) : (w[i >> 1] << 16));
+    }
+  } else if constexpr (kBytes == 8) {
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
+    if constexpr (sizeof(T) == 4) { f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); }
+    else { f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u); f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u); }
+  } else if constexpr (kBytes == 4 && sizeof(T) == 2) {
+    const uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(p));
+    f[0] = __uint_as_float(v << 16); f[1] = __uint_as_float(v & 0xffff0000u);
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) f[i] = ld_f<T>(p + i);
+  }
+}
 
 // grid (n_seqs, H, splits), kGqaDecWarps warps.  A warp takes 32 keys at a time: first every lane scores ONE key (a
-// thread-local dot product over D), then every lane owns value columns lane, lane + 32, .. and the 32 weights are
-// passed around by shuffle.  VPL = ceil(V / 32) accumulators per lane.
+// thread-local dot product over D, the key row read in 16-byte pieces where its alignment allows), then every lane owns
+// the VPL = ceil(V / 32) value columns lane VPL .. lane VPL + VPL - 1 (one vector load per key) and the 32 weights are
+// passed around by shuffle.
 template <typename T, int VPL>
 __global__ void __launch_bounds__(kGqaDecWarps * 32) gqa_decode_partial_kernel(const GqaDecodeArgs p, const Ragged rg) {
-  extern __shared__ float gd_sm[];
+  extern __shared__ __align__(16) float gd_sm[];
   const int s = blockIdx.x, hd = blockIdx.y, sp = blockIdx.z;
   const int row = rg.cu[s];
   if (rg.cu[s + 1] - row != 1) return;
   const int H = p.H, G = p.G, D = p.D, V = p.V, hpg = H / G, g = hd / hpg;
-  float* qs = gd_sm;                      // [D] query times scale
-  float* wp = gd_sm + D;                  // [warps][V + 2]
+  const int Dp = (D + 3) / 4 * 4;
+  float* qs = gd_sm;                      // [Dp] query times scale
+  float* wp = gd_sm + Dp;                 // [warps][V + 2]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const T* q = (const T*)p.q + (((size_t)g * rg.M + row) * hpg + (hd - g * hpg)) * D;
-  for (int d = tid; d < D; d += blockDim.x) qs[d] = ld_f<T>(q + d) * p.scale;
+  for (int d = tid; d < Dp; d += blockDim.x) qs[d] = d < D ? ld_f<T>(q + d) * p.scale : 0.f;
   __syncthreads();
   const int ctx = rg.pos0[s] + 1, per = (ctx + p.splits - 1) / p.splits;
   const int k_lo = sp * per, k_hi = min(ctx, k_lo + per);
   const size_t roww = (size_t)G * (D + V);
+  constexpr int kPer = 16 / (int)sizeof(T);
+  const bool pool16 = ((uintptr_t)p.cache & 15) == 0;
+  const bool vec_k = pool16 && D % kPer == 0 && roww % kPer == 0;
+  constexpr int kVecBytes = VPL * (int)sizeof(T) >= 16 ? 16 : VPL * (int)sizeof(T);
+  constexpr int kVecElems = kVecBytes / (int)sizeof(T);
+  const bool vec_v = pool16 && V % VPL == 0 && roww % kVecElems == 0 && ((size_t)G * D) % kVecElems == 0 && V % kVecElems == 0;
   float mx = -INFINITY, sum = 0.f, acc[VPL];
 #pragma unroll
   for (int i = 0; i < VPL; ++i) acc[i] = 0.f;
+  const int c0 = lane * VPL;  // first value column of this lane
   for (int k0 = k_lo + warp * 32; k0 < k_hi; k0 += kGqaDecWarps * 32) {
     const int key = k0 + lane;
     const bool ok = key < k_hi;
@@ -124,9 +163,21 @@ __global__ void __launch_bounds__(kGqaDecWarps * 32) gqa_decode_partial_kernel(c
     if (ok) {
       const T* kr = (const T*)p.cache + prow * roww + (size_t)g * D;
       float a0 = 0.f, a1 = 0.f;
-      int d = 0;
-      for (; d + 1 < D; d += 2) { a0 = fmaf(qs[d], ld_f<T>(kr + d), a0); a1 = fmaf(qs[d + 1], ld_f<T>(kr + d + 1), a1); }
-      if (d < D) a0 = fmaf(qs[d], ld_f<T>(kr + d), a0);
+      if (vec_k) {
+        for (int d = 0; d < D; d += kPer) {
+          float f[kPer];
+          ld_contig<T, kPer>(kr + d, f);
+#pragma unroll
+          for (int e = 0; e < kPer; e += 4) {
+            const float4 q4 = *reinterpret_cast<const float4*>(qs + d + e);
+            a0 = fmaf(q4.x, f[e], a0); a1 = fmaf(q4.y, f[e + 1], a1); a0 = fmaf(q4.z, f[e + 2], a0); a1 = fmaf(q4.w, f[e + 3], a1);
+          }
+        }
+      } else {
+        int d = 0;
+        for (; d + 1 < D; d += 2) { a0 = fmaf(qs[d], ld_f<T>(kr + d), a0); a1 = fmaf(qs[d + 1], ld_f<T>(kr + d + 1), a1); }
+        if (d < D) a0 = fmaf(qs[d], ld_f<T>(kr + d), a0);
+      }
       sc = a0 + a1;
     }
     const float m_new = fmaxf(mx, warp_max(sc));
@@ -140,20 +191,25 @@ __global__ void __launch_bounds__(kGqaDecWarps * 32) gqa_decode_partial_kernel(c
     for (int kk = 0; kk < nk; ++kk) {
       const float wk = __shfl_sync(0xffffffffu, w, kk);
       const unsigned long long pr = __shfl_sync(0xffffffffu, (unsigned long long)prow, kk);
-      const T* vr = (const T*)p.cache + (size_t)pr * roww + (size_t)G * D + (size_t)g * V;
+      const T* vr = (const T*)p.cache + (size_t)pr * roww + (size_t)G * D + (size_t)g * V + c0;
+      if (vec_v) {
+        if (c0 < V) {
+          float f[VPL];
+          ld_contig<T, VPL>(vr, f);
 #pragma unroll
-      for (int i = 0; i < VPL; ++i) {
-        const int c = lane + 32 * i;
-        if (c < V) acc[i] = fmaf(wk, ld_f<T>(vr + c), acc[i]);
+          for (int i = 0; i < VPL; ++i) acc[i] = fmaf(wk, f[i], acc[i]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < VPL; ++i)
+          if (c0 + i < V) acc[i] = fmaf(wk, ld_f<T>(vr + i), acc[i]);
       }
     }
   }
   float* mine = wp + (size_t)warp * (V + 2);
 #pragma unroll
-  for (int i = 0; i < VPL; ++i) {
-    const int c = lane + 32 * i;
-    if (c < V) mine[c] = acc[i];
-  }
+  for (int i = 0; i < VPL; ++i)
+    if (c0 + i < V) mine[c0 + i] = acc[i];
   if (lane == 0) { mine[V] = mx; mine[V + 1] = sum; }
   __syncthreads();
   // the warps' parts are joined in warp order

@@ -528,7 +528,8 @@ struct HybRun {
     a.u = e->p1; a.ld_u = R; a.gates = e->p2; a.ld_g = 2 * R; a.gate_bias = Lr.t[SSDK_HT_RGLRU_GATE_B].p; a.lam = Lr.t[SSDK_HT_RGLRU_LAM].p;
     a.y = e->p0; a.ld_y = 2 * R; a.y_bias = Lr.t[SSDK_HT_RGLRU_IN_B].p; a.out = e->t1; a.S = st; a.slot_stride = e->slot_floats;
     a.R = R; a.bs = bs; a.decay_mult = c.decay_mult;
-    CKI(L.go(ssdk::rglru_scan_kernel<T>, dim3(rg.n_seqs, (R + 127) / 128), dim3(128), 0, a, rg));
+    const int rt = rg.n_seqs * ((R + 127) / 128) >= num_sms() ? 128 : 32;  // few sequences: one warp per CTA spreads the channels over the SMs
+    CKI(L.go(ssdk::rglru_scan_kernel<T>, dim3(rg.n_seqs, (R + rt - 1) / rt), dim3(rt), 0, a, rg));
     return lin(e->t1, R, Lr.t[SSDK_HT_MIX_OUT].p, R, e->mix_out, W, M, W, R);
   }
 
@@ -560,12 +561,15 @@ struct HybRun {
     a.x = e->p1; a.ld_x = I; a.dtz = dtz; a.ld_dt = I; a.dt_bias = Lr.t[SSDK_HT_SEL_DT_B].p; a.bc = e->p2 + Rk; a.ld_bc = Nx;
     a.A_log = Lr.t[SSDK_HT_SEL_ALOG].p; a.Dw = Lr.t[SSDK_HT_SEL_D].p; a.z = e->p0 + I; a.ld_z = 2 * I; a.out = e->t1;
     a.S = st; a.slot_stride = e->slot_floats; a.inner = I; a.N = N;
-    const dim3 grid(rg.n_seqs, (I + 127) / 128), block(128);
     const size_t smem = (size_t)ssdk::kSelRows * 2 * N * 4;
-    if (N <= 16) CKI(L.go(ssdk::selective_scan_kernel<T, 16>, grid, block, smem, a, rg));
-    else if (N <= 32) CKI(L.go(ssdk::selective_scan_kernel<T, 32>, grid, block, smem, a, rg));
-    else if (N <= 64) CKI(L.go(ssdk::selective_scan_kernel<T, 64>, grid, block, smem, a, rg));
-    else CKI(L.go(ssdk::selective_scan_kernel<T, 0>, grid, block, smem, a, rg));
+    if (N <= 128) {  // four states per lane, the lanes of a channel side by side in one warp
+      int lpc = 1;
+      while (lpc * 4 < N) lpc *= 2;
+      const int cpb = 128 / lpc;
+      CKI(L.go(ssdk::selective_scan_kernel<T, 4>, dim3(rg.n_seqs, (I + cpb - 1) / cpb), dim3(lpc, cpb), smem, a, rg));
+    } else {
+      CKI(L.go(ssdk::selective_scan_kernel<T, 0>, dim3(rg.n_seqs, (I + 127) / 128), dim3(1, 128), smem, a, rg));
+    }
     return lin(e->t1, I, Lr.t[SSDK_HT_MIX_OUT].p, I, e->mix_out, W, M, W, I);
   }
 
@@ -651,16 +655,21 @@ struct HybRun {
     ssdk::DeltaArgs da;
     da.q = dp.q; da.k = dp.k; da.v = dp.v; da.beta = dp.beta; da.decay = dp.decay; da.o = e->p1; da.S = st; da.slot_stride = e->slot_floats;
     da.H = Hd; da.G = Gd; da.D = Dd; da.V = Vd;
-    const int Vr = (Vd + 31) / 32 * 32;
-    int DR = 0, NG = 1;
+    const int Vall = (Vd + 31) / 32 * 32;
+    int Vr = Vall, DR = 0, NG = 1;
     delta_shape(Dd, Vr, &DR, &NG);
-    const dim3 grid(rg.n_seqs, Hd), block(Vr, NG);
+    // the state's columns are independent: few (sequence, head) pairs spread a head's columns over several CTAs
+    while (DR > 0 && Vr % 64 == 0 && rg.n_seqs * Hd * (Vall / Vr) < num_sms()) {
+      Vr /= 2;
+      delta_shape(Dd, Vr, &DR, &NG);
+    }
+    const dim3 grid(rg.n_seqs, Hd, (Vall + Vr - 1) / Vr), block(Vr, NG);
     const size_t smem = ssdk::delta_scan_smem(Dd, Vr, DR, NG);
     if (DR == 16) CKI(L.go(ssdk::delta_scan_kernel<16>, grid, block, smem, da, rg));
     else if (DR == 32) CKI(L.go(ssdk::delta_scan_kernel<32>, grid, block, smem, da, rg));
     else if (DR == 64) CKI(L.go(ssdk::delta_scan_kernel<64>, grid, block, smem, da, rg));
     else CKI(L.go(ssdk::delta_scan_kernel<0>, grid, block, smem, da, rg));
-    CKI(L.go(ssdk::head_rmsnorm_gate_kernel<T, 0>, dim3(M, Hd), dim3(std::min(256, Vr)), 0, (const float*)e->p1, (const float*)(e->p0 + o_dg), Ntot,
+    CKI(L.go(ssdk::head_rmsnorm_gate_kernel<T, 0>, dim3(M, Hd), dim3(std::min(256, Vall)), 0, (const float*)e->p1, (const float*)(e->p0 + o_dg), Ntot,
              (const T*)Lr.t[SSDK_HT_MIX_NORM].p, (T*)e->t1, Hd, Vd, e->cfg.eps));
     return lin(e->t1, dHV, Lr.t[SSDK_HT_MIX_OUT].p, dHV, e->mix2, W, M, W, dHV);
   }

@@ -314,8 +314,39 @@ def random_hybrid_weights(spec: HybridSpec, dtype: torch.dtype, device, seed: in
 
     w = {"EMBED": torch.randn(spec.vocab, W, generator=g, device=device).to(dtype), "HEAD": lin(spec.vocab, W),
          "FINAL_NORM": vec(W), "layers": []}
+    def uni(lo, hi, *shape):
+        return (lo + (hi - lo) * torch.rand(*shape, generator=g, device=device)).to(dtype)
+
+    if spec.block == L.BLOCK_SERIAL_POSTNORM:
+        w["FINAL_NORM"] = vec(W, 1.0)
     for ls in spec.layers:
         H, D, V = ls.heads, ls.dim, ls.vdim
+        if ls.mixer in ("rglru", "mamba1", "parallel"):
+            lw = {"NORM": vec(W, 1.0)}
+            taps = ls.conv
+            if ls.mixer == "rglru":
+                R, bs = ls.inner, ls.inner // ls.blocks
+                lw["RGLRU_IN"], lw["RGLRU_IN_B"] = lin(2 * R, W), vec(2 * R, 0.0, 0.3)
+                lw["CONV_W"], lw["CONV_B"] = (torch.randn(R, taps, generator=g, device=device) * 0.5).to(dtype), vec(R, 0.0, 0.2)
+                lw["RGLRU_GATE"], lw["RGLRU_GATE_B"] = lin(ls.blocks, 2 * bs, bs), vec(ls.blocks * 2 * bs, 0.0, 0.5).view(ls.blocks, 2 * bs)
+                lw["RGLRU_LAM"], lw["MIX_OUT"] = uni(-4.0, 0.5, R), lin(W, R)
+            elif ls.mixer == "mamba1":
+                I, N, Rk = ls.inner, ls.state, ls.dt_rank
+                lw["SEL_IN"], lw["CONV_B"] = lin(2 * I, W), vec(I, 0.0, 0.2)
+                lw["CONV_W"] = (torch.randn(I, taps, generator=g, device=device) * 0.5).to(dtype)
+                lw["SEL_X"], lw["SEL_DT"], lw["SEL_DT_B"] = lin(Rk + 2 * N, I), lin(I, Rk), uni(-3.0, -0.5, I)
+                lw["SEL_ALOG"], lw["SEL_D"], lw["MIX_OUT"] = torch.log(uni(0.3, 4.0, I, N).float()).to(dtype), vec(I, 1.0, 0.2), lin(W, I)
+            else:
+                G, Hd, Gd, Dd, Vd = ls.kv_heads, ls.d_heads, ls.d_kv_heads, ls.d_dim, ls.d_vdim
+                Cd = 2 * Gd * Dd + Hd * Vd
+                lw["PAIR_IN"] = lin(H * D + G * D + G * V + H * V + Cd + Hd * Vd + 2 * Hd, W)
+                lw["ATTN_OUT"], lw["MIX_OUT"] = lin(W, H * V), lin(W, Hd * Vd)
+                lw["CONV_W"] = (torch.randn(Cd, taps, generator=g, device=device) * 0.6).to(dtype)
+                lw["DELTA_ALOG"], lw["DELTA_DT_B"], lw["MIX_NORM"] = uni(-2.0, 0.5, Hd), uni(-2.0, 1.0, Hd), vec(Hd * Vd, 1.0)
+            if ls.mlp == "dense":
+                lw["NORM2"], lw["GLU_IN"], lw["GLU_OUT"] = vec(W, 1.0), lin(2 * ls.ff, W), lin(W, ls.ff)
+            w["layers"].append(lw)
+            continue
         lw = {"NORM": vec(W), "LS_MIX": vec(W, 1.0), "MIX_OUT": lin(W, H * V)}
         if ls.mixer == "wkv":
             lw["WKV_MU"] = torch.rand(5, W, generator=g, device=device).to(dtype)

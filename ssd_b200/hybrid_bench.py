@@ -1,4 +1,8 @@
-"""Throughput of the hybrid family beside the closest dense model of the framework (bench.py --arch pikavik).
+"""Throughput of the hybrid families (bench.py --arch pikavik | kefurax).
+
+--arch pikavik: a Pikavik stack beside the closest dense model of the framework (below).
+--arch kefurax: a Kefurax stack (attention + delta-rule pair with a dense feed-forward, selective scan, rglru, ...) beside
+the closest existing model of the framework, a Pikavik stack of the same width, depth and active feed-forward size.
 
 For every size: a Pikavik stack (mLSTM, wkv, wkv, latent attention, ... each with a grouped mixture of experts and a
 shared expert) with random weights, and a Llama stack of the same width, depth and ACTIVE feed-forward size
@@ -37,6 +41,27 @@ def pikavik_spec(z):
     return HybridSpec(z["width"], z["vocab"], 1e-6, layers)
 
 
+def kefurax_spec(z):
+    """Layers that resemble a real model's: 128-wide heads, four query heads per key/value head, a delta rule with
+    128 x 128 heads, a selective scan of twice the width with 16 states, a recurrence as wide as the model."""
+    from .hybrid import RGLRU_DECAY_MULT, HybridSpec, LayerSpec
+    W = z["width"]
+    heads, ff = W // 128, z["top"] * z["ff"] + z["sff"]
+    layers = []
+    for i in range(z["layers"]):
+        kind = ("parallel", "mamba1", "rglru", "parallel")[i % 4]
+        if kind == "parallel":
+            layers.append(LayerSpec("parallel", heads, 128, 128, rot_dims=64, rot_base=10000.0, attn_scale=128 ** -0.5,
+                                    kv_heads=max(1, heads // 4), qk_norm=1, sink=1.0, yarn_factor=4.0, yarn_original=4096.0,
+                                    yarn_fast=16.0, yarn_slow=2.0, conv=4, d_heads=heads, d_kv_heads=max(1, heads // 2), d_dim=128,
+                                    d_vdim=128, left_scale=1.0, right_scale=1.0, mlp="dense", ff=ff))
+        elif kind == "mamba1":
+            layers.append(LayerSpec("mamba1", 1, 1, inner=2 * W, state=16, dt_rank=W // 16, conv=4, mlp="dense", ff=ff))
+        else:
+            layers.append(LayerSpec("rglru", 1, 1, inner=W, blocks=heads, conv=4, decay_mult=RGLRU_DECAY_MULT, mlp="dense", ff=ff))
+    return HybridSpec(W, z["vocab"], 1e-6, layers, architecture="Kefurax", embed_scale=1.0, residual_mult=0.7)
+
+
 def _events(fn, warmup, steps):
     for _ in range(warmup):
         fn()
@@ -52,9 +77,9 @@ def _events(fn, warmup, steps):
     return float(np.median(t))
 
 
-def run_pikavik(z, prompt, batch, warmup, steps, dtype="bfloat16"):
+def run_pikavik(z, prompt, batch, warmup, steps, dtype="bfloat16", spec_fn=pikavik_spec):
     from .hybrid import HybridRunner, random_hybrid_weights
-    spec = pikavik_spec(z)
+    spec = spec_fn(z)
     tdt = torch.bfloat16 if dtype == "bfloat16" else torch.float32
     w = random_hybrid_weights(spec, tdt, "cuda:0")
     bs = 64
@@ -74,7 +99,7 @@ def run_pikavik(z, prompt, batch, warmup, steps, dtype="bfloat16"):
                                     temps=[0.0] * batch), warmup, steps)
     launches_decode = (r.launch_count - n0) // (warmup + steps)
     params = sum(t.numel() for lw in w["layers"] for t in lw.values()) + w["HEAD"].numel()
-    active = params - sum(lw["EXPERT_IN"].numel() + lw["EXPERT_OUT"].numel() for lw in w["layers"]) * (1 - z["top"] / z["experts"])
+    active = params - sum(lw["EXPERT_IN"].numel() + lw["EXPERT_OUT"].numel() for lw in w["layers"] if "EXPERT_IN" in lw) * (1 - z["top"] / z["experts"])
     r.close()
     return {"prefill_ms": pre, "prefill_tok_s": prompt / pre * 1e3, "decode_ms": dec, "decode_tok_s": batch / dec * 1e3,
             "launches_prefill": launches_prefill, "launches_decode": launches_decode, "params": int(params),
@@ -124,7 +149,27 @@ def run_llama(z, prompt, batch, warmup, steps):
             "active_params": int(params)}
 
 
+def run_kefurax(args):
+    out = {"metric": "prefill and decode tokens/s, Kefurax beside Pikavik at equal width / depth / active feed-forward",
+           "dtype": "bf16", "data": "synthetic (random weights, random token ids)", "n_gpus": 1, "steps": args.steps,
+           "warmup": args.warmup, "timing": "CUDA events around the public forward call, median; every pass streams the stack's "
+           "weights (> 126 MB L2 for size m; size s partly L2-resident, stated here)", "sizes": {}}
+    names = [args.hybrid_size] if args.hybrid_size != "all" else list(SIZES)
+    for name in names:
+        z = SIZES[name]
+        row = {"config": {k: z[k] for k in ("width", "layers", "vocab")}, "prompt": args.prompt_len_hybrid, "decode_batch": args.hybrid_batch}
+        row["kefurax"] = run_pikavik(z, args.prompt_len_hybrid, args.hybrid_batch, args.warmup, args.steps, spec_fn=kefurax_spec)
+        if not args.no_dense_arm:
+            row["pikavik"] = run_pikavik(z, args.prompt_len_hybrid, args.hybrid_batch, args.warmup, args.steps)
+        if args.hybrid_fp32:
+            row["kefurax_fp32"] = run_pikavik(z, args.prompt_len_hybrid, args.hybrid_batch, args.warmup, args.steps, "float32", kefurax_spec)
+        out["sizes"][name] = row
+    return out
+
+
 def run(args):
+    if getattr(args, "arch", "pikavik") == "kefurax":
+        return run_kefurax(args)
     out = {"metric": "prefill and decode tokens/s, Pikavik beside Llama at equal width / depth / active feed-forward",
            "dtype": "bf16", "data": "synthetic (random weights, random token ids)", "n_gpus": 1, "steps": args.steps,
            "warmup": args.warmup, "timing": "CUDA events around the public forward call, median; every pass streams the stack's "

@@ -48,6 +48,7 @@ MIXERS = {
     "mamba1": U.mamba1(),
     "mamba1-state-40": U.mamba1(inner=12, state=40, dt_rank=1, conv=4),
     "mamba1-state-70": U.mamba1(inner=9, state=70, dt_rank=4, conv=2),
+    "mamba1-state-beyond-registers": U.mamba1(inner=5, state=130, dt_rank=2, conv=3),
     "pair": U.parallel(),
     "pair-attention-only": U.parallel(right_scale=0.0),
     "pair-delta-only": U.parallel(left_scale=0.0),
