@@ -14,6 +14,7 @@
 // A state slot is never cleared: a sequence whose portion starts at position 0 ignores what the slot holds.
 #pragma once
 #include "layer_ops.cuh"
+#include "recurrent.cuh"  // cp_async4
 
 namespace ssdk {
 
@@ -94,10 +95,11 @@ __global__ void cast_cols_kernel(const float* __restrict__ src, int ld_src, T* _
 // ---------------------------------------------------------------------------------------------- rglru
 struct RglruArgs {
   const float* u; int ld_u;          // [M, R] convolved x branch
-  const float* gates; int ld_g;      // [M, blocks * 2 bs]: per block recurrence-gate pre-activations, then input-gate ones
+  const float* gates; int ld_g;      // [M, blocks * 2 bs]: per block recurrence-gate slots, then input-gate slots
+                                     // (pre-activations before rglru_gate_kernel, decay a and input term b after it)
   const void* gate_bias;             // [blocks, 2 bs] T
   const void* lam;                   // [R] T
-  const float* y; int ld_y;          // [M, ...] y-branch pre-activation without its bias
+  const float* y; int ld_y;          // [M, ...] y branch (pre-activation before rglru_gate_kernel, gelu after)
   const void* y_bias;                // [R] T
   void* out;                         // [M, R] T: S * gelu_tanh(y)
   float* S; size_t slot_stride;      // [R] per slot
@@ -105,39 +107,45 @@ struct RglruArgs {
   float decay_mult;
 };
 
-constexpr int kRglruRows = 8;  // rows whose inputs are requested together
+// grid (M, ceil(R / blockDim)): everything of a row that does not depend on the state, for all rows at once and in place:
+// gates[m][recurrence slot] <- a = exp(-c r softplus(lam)), gates[m][input slot] <- sqrt(1 - a^2) i u,
+// y[m] <- gelu_tanh(y[m] + bias)
+template <typename T>
+__global__ void rglru_gate_kernel(const RglruArgs p, float* __restrict__ gates, float* __restrict__ y) {
+  const int m = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= p.R) return;
+  const int b = c / p.bs, cb = c - b * p.bs;
+  const int gr = b * 2 * p.bs + cb, gi = gr + p.bs;
+  const float sp = softplus_f(ld_f<T>((const T*)p.lam + c)) * p.decay_mult;
+  float* grow = gates + (size_t)m * p.ld_g;
+  const float log_a = -sigmoid_f(grow[gr] + ld_f<T>((const T*)p.gate_bias + gr)) * sp;
+  const float i = sigmoid_f(grow[gi] + ld_f<T>((const T*)p.gate_bias + gi));
+  grow[gr] = expf(log_a);
+  // 1 - a^2 through expm1: exact also where a is within an ulp of 1
+  grow[gi] = sqrtf(-expm1f(2.0f * log_a)) * i * p.u[(size_t)m * p.ld_u + c];
+  float* yp = y + (size_t)m * p.ld_y + c;
+  *yp = gelu_tanh_f(*yp + ld_f<T>((const T*)p.y_bias + c));
+}
 
-// grid (n_seqs, ceil(R / blockDim)): one thread per channel walks its sequence's rows.  Rows are taken eight at a time:
-// their loads are issued together and everything that does not depend on the state (both gates, the decay, the input's
-// weight, the gelu branch) is evaluated for the eight rows side by side; only S = a S + b runs in sequence.
+constexpr int kRglruRows = 16;  // rows whose operands are requested together
+
+// grid (n_seqs, ceil(R / blockDim)): one thread per channel walks its sequence's rows, S = a S + b, out = S y, with the
+// operands rglru_gate_kernel left (sixteen rows' loads in flight at a time).
 template <typename T>
 __global__ void rglru_scan_kernel(const RglruArgs p, const Ragged rg) {
   const int s = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= p.R) return;
   const int b = c / p.bs, cb = c - b * p.bs;
   const int gr = b * 2 * p.bs + cb, gi = gr + p.bs;
-  const float rb = ld_f<T>((const T*)p.gate_bias + gr), ib = ld_f<T>((const T*)p.gate_bias + gi);
-  const float sp = softplus_f(ld_f<T>((const T*)p.lam + c)) * p.decay_mult;
-  const float yb = ld_f<T>((const T*)p.y_bias + c);
   float* Sp = p.S + (size_t)rg.slot[s] * p.slot_stride + c;
   float S = rg.pos0[s] > 0 ? *Sp : 0.f;
   const int r0 = rg.cu[s], r1 = rg.cu[s + 1];
   for (int m0 = r0; m0 < r1; m0 += kRglruRows) {
-    float zr[kRglruRows], zi[kRglruRows], u[kRglruRows], y[kRglruRows];
+    float a[kRglruRows], bb[kRglruRows], y[kRglruRows];
 #pragma unroll
     for (int k = 0; k < kRglruRows; ++k) {
       const int m = min(m0 + k, r1 - 1);
-      zr[k] = p.gates[(size_t)m * p.ld_g + gr]; zi[k] = p.gates[(size_t)m * p.ld_g + gi];
-      u[k] = p.u[(size_t)m * p.ld_u + c]; y[k] = p.y[(size_t)m * p.ld_y + c];
-    }
-    float a[kRglruRows], bb[kRglruRows];
-#pragma unroll
-    for (int k = 0; k < kRglruRows; ++k) {
-      const float log_a = -sigmoid_f(zr[k] + rb) * sp;
-      a[k] = expf(log_a);
-      // 1 - a^2 through expm1: exact also where a is within an ulp of 1
-      bb[k] = sqrtf(-expm1f(2.0f * log_a)) * sigmoid_f(zi[k] + ib) * u[k];
-      y[k] = gelu_tanh_f(y[k] + yb);
+      a[k] = p.gates[(size_t)m * p.ld_g + gr]; bb[k] = p.gates[(size_t)m * p.ld_g + gi]; y[k] = p.y[(size_t)m * p.ld_y + c];
     }
 #pragma unroll
     for (int k = 0; k < kRglruRows; ++k) {
@@ -153,24 +161,35 @@ __global__ void rglru_scan_kernel(const RglruArgs p, const Ragged rg) {
 // ---------------------------------------------------------------------------------------------- selective scan
 struct SelScanArgs {
   const float* x; int ld_x;          // [M, inner] convolved, SiLU'd input
-  const float* dtz; int ld_dt;       // [M, inner] step-size pre-activation without its bias
-  const void* dt_bias;               // [inner] T
+  const float* dtz; int ld_dt;       // [M, inner] step sizes (after softplus)
   const float* bc; int ld_bc;        // [M, ...]: B in columns [0, N), C in [N, 2N)
   const void* A_log;                 // [inner, N] T
   const void* Dw;                    // [inner] T
-  const float* z; int ld_z;          // [M, inner] gate pre-activation
+  const float* z; int ld_z;          // [M, inner] gate values silu(z)
   void* out;                         // [M, inner] T: y * silu(z)
   float* S; size_t slot_stride;      // [inner, N] per slot
   int inner, N;
 };
+
+// grid (M, ceil(inner / blockDim)): the state-independent part of a row, in place: dtz <- softplus(dtz + bias), z <- silu(z)
+template <typename T>
+__global__ void selective_gate_kernel(float* __restrict__ dtz, int ld_dt, const T* __restrict__ dt_bias, float* __restrict__ z, int ld_z,
+                                      int inner) {
+  const int m = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= inner) return;
+  float* d = dtz + (size_t)m * ld_dt + c;
+  *d = softplus_f(*d + ld_f<T>(dt_bias + c));
+  float* zp = z + (size_t)m * ld_z + c;
+  *zp = silu_f(*zp);
+}
 
 constexpr int kSelRows = 8;  // rows whose inputs are requested (and whose B | C are staged) together
 
 // A channel's N states are spread over LPC = blockDim.x lanes of a warp (a power of two), NT states per lane in
 // registers (N <= NT * LPC); blockDim.y channels per CTA, grid (n_seqs, ceil(inner / blockDim.y)).  Per row a lane
 // advances its states and the lanes' parts of y = sum_n S[n] C[n] meet by shuffle (a fixed tree).  exp(dt A) is taken as
-// exp2(dt (A log2 e)).  NT == 0: any N, one lane per channel, the state stays in its slot (global memory).
-// dynamic shared memory: kSelRows * 2 N floats.
+// exp2(dt (A log2 e)).  dtz holds the step sizes and z the gate values selective_gate_kernel left.  NT == 0: any N, one
+// lane per channel, the state stays in its slot (global memory).  dynamic shared memory: kSelRows * 2 N floats.
 template <typename T, int NT>
 __global__ void selective_scan_kernel(const SelScanArgs p, const Ragged rg) {
   extern __shared__ float sel_sm[];
@@ -191,7 +210,7 @@ __global__ void selective_scan_kernel(const SelScanArgs p, const Ragged rg) {
   } else if (live && !carried) {
     for (int n = 0; n < N; ++n) Sg[n] = 0.f;
   }
-  const float dtb = live ? ld_f<T>((const T*)p.dt_bias + c) : 0.f, Dc = live ? ld_f<T>((const T*)p.Dw + c) : 0.f;
+  const float Dc = live ? ld_f<T>((const T*)p.Dw + c) : 0.f;
   const int r0 = rg.cu[s], r1 = rg.cu[s + 1], cc = live ? c : 0;
   for (int m0 = r0; m0 < r1; m0 += kSelRows) {
     const int nr = min(kSelRows, r1 - m0);
@@ -207,11 +226,6 @@ __global__ void selective_scan_kernel(const SelScanArgs p, const Ragged rg) {
       sel_sm[i] = p.bc[(size_t)(m0 + r) * p.ld_bc + k];
     }
     __syncthreads();
-#pragma unroll
-    for (int r = 0; r < kSelRows; ++r) {
-      dt[r] = softplus_f(dt[r] + dtb);
-      zv[r] = silu_f(zv[r]);
-    }
 #pragma unroll
     for (int r = 0; r < kSelRows; ++r) {
       if (r < nr) {
@@ -299,12 +313,12 @@ struct DeltaArgs {
   int H, G, D, V;
 };
 
-constexpr int kDeltaRows = 8;  // rows staged together
+constexpr int kDeltaRows = 16;  // rows staged together (two such buffers: the next chunk arrives under the current one's walk)
 
 // shared memory of delta_scan_kernel<DR> with G row groups (DR == 0: G = 1 and the state itself lives there)
 inline size_t delta_scan_smem(int D, int Vr, int DR, int G) {
   const int DP = DR > 0 ? DR * G : D;
-  return ((size_t)(DR > 0 ? 0 : D * Vr) + (size_t)kDeltaRows * (2 * DP + Vr + 2) + (size_t)2 * G * Vr) * 4;
+  return ((size_t)(DR > 0 ? 0 : D * Vr) + (size_t)2 * kDeltaRows * (2 * DP + Vr + 2) + (size_t)2 * G * Vr) * 4;
 }
 
 // grid (n_seqs, H, column splits), block (Vr, G) with Vr a multiple of 32 columns per CTA (the columns of the state are
@@ -321,10 +335,10 @@ __global__ void delta_scan_kernel(const DeltaArgs p, const Ragged rg) {
   const int j = blockIdx.z * Vr + jl;  // column of the head's state
   const int D = p.D, V = p.V, DP = DR > 0 ? DR * NG : D;
   float* Ssm = ds_sm;                                     // [D][Vr] (DR == 0)
-  float* kq = ds_sm + (DR > 0 ? 0 : (size_t)D * Vr);      // [rows][2 DP]: k then q
-  float* vs = kq + kDeltaRows * 2 * DP;                   // [rows][Vr]
-  float* bg = vs + kDeltaRows * Vr;                       // [rows][2]: beta, decay
-  float* part = bg + kDeltaRows * 2;                      // [2][NG][Vr] partial contractions
+  constexpr int kR = kDeltaRows;
+  const int stage = kR * (2 * DP + Vr + 2);               // floats of one staging buffer
+  float* st0 = ds_sm + (DR > 0 ? 0 : (size_t)D * Vr);     // two buffers: [rows][2 DP] k then q | [rows][Vr] v | [rows][2] beta, decay
+  float* part = st0 + 2 * stage;                          // [2][NG][Vr] partial contractions
   float Sr[DR > 0 ? DR : 1];
   const bool col = j < V, carried = rg.pos0[s] > 0;
   const int d0 = gi * DR;
@@ -335,25 +349,45 @@ __global__ void delta_scan_kernel(const DeltaArgs p, const Ragged rg) {
   } else {
     for (int d = 0; d < D; ++d) Ssm[(size_t)d * Vr + jl] = (col && carried) ? Sg[(size_t)d * V] : 0.f;
   }
+  // padding (rows of k and q from D up to DP, value columns beyond V) is zero in both buffers and never written again
+  for (int i = tid; i < 2 * stage; i += nthr) st0[i] = 0.f;
+  __syncthreads();
   const int r0 = rg.cu[s], r1 = rg.cu[s + 1], GD = p.G * D, HV = p.H * V;
-  for (int m0 = r0; m0 < r1; m0 += kDeltaRows) {
-    const int nr = min(kDeltaRows, r1 - m0);
-    __syncthreads();
-    for (int i = tid; i < nr * DP; i += nthr) {
-      const int r = i / DP, d = i - r * DP;
-      kq[r * 2 * DP + d] = d < D ? p.k[(size_t)(m0 + r) * GD + g * D + d] : 0.f;
-      kq[r * 2 * DP + DP + d] = d < D ? p.q[(size_t)(m0 + r) * GD + g * D + d] : 0.f;
+  const int vcols = max(0, min(Vr, V - (int)blockIdx.z * Vr));
+  auto issue = [&](int m0, float* buf) {  // 4-byte asynchronous copies: no alignment rule beyond the element's own
+    const int nr = min(kR, r1 - m0);
+    float* kq = buf;
+    float* vs = kq + kR * 2 * DP;
+    float* bg = vs + kR * Vr;
+    for (int i = tid; i < nr * D; i += nthr) {
+      const int r = i / D, d = i - r * D;
+      cp_async4(kq + r * 2 * DP + d, p.k + (size_t)(m0 + r) * GD + g * D + d);
+      cp_async4(kq + r * 2 * DP + DP + d, p.q + (size_t)(m0 + r) * GD + g * D + d);
     }
-    for (int i = tid; i < nr * Vr; i += nthr) {
-      const int r = i / Vr, c = i - r * Vr;
-      const int cg = blockIdx.z * Vr + c;
-      vs[i] = cg < V ? p.v[(size_t)(m0 + r) * HV + hd * V + cg] : 0.f;
+    for (int i = tid; i < nr * vcols; i += nthr) {
+      const int r = i / vcols, c = i - r * vcols;
+      cp_async4(vs + r * Vr + c, p.v + (size_t)(m0 + r) * HV + hd * V + blockIdx.z * Vr + c);
     }
     if (tid < nr) {
-      bg[2 * tid] = p.beta[(size_t)(m0 + tid) * p.H + hd];
-      bg[2 * tid + 1] = p.decay[(size_t)(m0 + tid) * p.H + hd];
+      cp_async4(bg + 2 * tid, p.beta + (size_t)(m0 + tid) * p.H + hd);
+      cp_async4(bg + 2 * tid + 1, p.decay + (size_t)(m0 + tid) * p.H + hd);
+    }
+    cp_async_commit();
+  };
+  issue(r0, st0);
+  int cur = 0;
+  for (int m0 = r0; m0 < r1; m0 += kR, cur ^= 1) {
+    const int nr = min(kR, r1 - m0);
+    if (m0 + kR < r1) {
+      issue(m0 + kR, st0 + (cur ^ 1) * stage);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
     __syncthreads();
+    const float* kq = st0 + cur * stage;
+    const float* vs = kq + kR * 2 * DP;
+    const float* bg = vs + kR * Vr;
     for (int r = 0; r < nr; ++r) {
       const float* kr = kq + r * 2 * DP + d0;
       const float* qr = kr + DP;
@@ -411,6 +445,7 @@ __global__ void delta_scan_kernel(const DeltaArgs p, const Ragged rg) {
       }
       if (col && gi == 0) p.o[(size_t)(m0 + r) * HV + hd * V + j] = o;
     }
+    __syncthreads();  // every thread is done with this buffer before the chunk after next is copied into it
   }
   if (col) {
     if (DR > 0) {

@@ -528,6 +528,7 @@ struct HybRun {
     a.u = e->p1; a.ld_u = R; a.gates = e->p2; a.ld_g = 2 * R; a.gate_bias = Lr.t[SSDK_HT_RGLRU_GATE_B].p; a.lam = Lr.t[SSDK_HT_RGLRU_LAM].p;
     a.y = e->p0; a.ld_y = 2 * R; a.y_bias = Lr.t[SSDK_HT_RGLRU_IN_B].p; a.out = e->t1; a.S = st; a.slot_stride = e->slot_floats;
     a.R = R; a.bs = bs; a.decay_mult = c.decay_mult;
+    CKI(L.go(ssdk::rglru_gate_kernel<T>, dim3(M, (R + 255) / 256), dim3(256), 0, a, e->p2, e->p0));
     const int rt = rg.n_seqs * ((R + 127) / 128) >= num_sms() ? 128 : 32;  // few sequences: one warp per CTA spreads the channels over the SMs
     CKI(L.go(ssdk::rglru_scan_kernel<T>, dim3(rg.n_seqs, (R + rt - 1) / rt), dim3(rt), 0, a, rg));
     return lin(e->t1, R, Lr.t[SSDK_HT_MIX_OUT].p, R, e->mix_out, W, M, W, R);
@@ -558,15 +559,23 @@ struct HybRun {
       CKI(lin(e->t1, Rk, Lr.t[SSDK_HT_SEL_DT].p, Rk, dtz, I, M, I, Rk));
     }
     ssdk::SelScanArgs a;
-    a.x = e->p1; a.ld_x = I; a.dtz = dtz; a.ld_dt = I; a.dt_bias = Lr.t[SSDK_HT_SEL_DT_B].p; a.bc = e->p2 + Rk; a.ld_bc = Nx;
+    a.x = e->p1; a.ld_x = I; a.dtz = dtz; a.ld_dt = I; a.bc = e->p2 + Rk; a.ld_bc = Nx;
     a.A_log = Lr.t[SSDK_HT_SEL_ALOG].p; a.Dw = Lr.t[SSDK_HT_SEL_D].p; a.z = e->p0 + I; a.ld_z = 2 * I; a.out = e->t1;
     a.S = st; a.slot_stride = e->slot_floats; a.inner = I; a.N = N;
     const size_t smem = (size_t)ssdk::kSelRows * 2 * N * 4;
-    if (N <= 128) {  // four states per lane, the lanes of a channel side by side in one warp
-      int lpc = 1;
-      while (lpc * 4 < N) lpc *= 2;
-      const int cpb = 128 / lpc;
-      CKI(L.go(ssdk::selective_scan_kernel<T, 4>, dim3(rg.n_seqs, (I + cpb - 1) / cpb), dim3(lpc, cpb), smem, a, rg));
+    CKI(L.go(ssdk::selective_gate_kernel<T>, dim3(M, (I + 255) / 256), dim3(256), 0, dtz, I, (const T*)Lr.t[SSDK_HT_SEL_DT_B].p, e->p0 + I, 2 * I, I));
+    if (N <= 128) {
+      // NT states per lane, the lanes of a channel side by side in one warp: the fewest lanes that still give every SM
+      // eight warps (a long prompt of one sequence), never more than a warp per channel
+      int nt = 4;
+      auto lanes = [&](int t) { int l = 1; while (l * t < N) l *= 2; return l; };
+      while (nt > 1 && (lanes(nt) > 32 || (long long)rg.n_seqs * I * lanes(nt) / 32 < 8LL * num_sms()) && lanes(nt / 2) <= 32) nt /= 2;
+      if (lanes(nt) > 32) nt = 4;
+      const int lpc = lanes(nt), cpb = 128 / lpc;
+      const dim3 grid(rg.n_seqs, (I + cpb - 1) / cpb), block(lpc, cpb);
+      if (nt == 4) CKI(L.go(ssdk::selective_scan_kernel<T, 4>, grid, block, smem, a, rg));
+      else if (nt == 2) CKI(L.go(ssdk::selective_scan_kernel<T, 2>, grid, block, smem, a, rg));
+      else CKI(L.go(ssdk::selective_scan_kernel<T, 1>, grid, block, smem, a, rg));
     } else {
       CKI(L.go(ssdk::selective_scan_kernel<T, 0>, dim3(rg.n_seqs, (I + 127) / 128), dim3(1, 128), smem, a, rg));
     }

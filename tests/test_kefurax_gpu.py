@@ -58,7 +58,7 @@ MIXERS = {
     "pair-no-rotation": U.parallel(left=U.attention(heads=2, kv_heads=2, dim=5, vdim=5, dims=0)),
     "pair-wide-delta-head": U.parallel(right=U.delta(heads=2, kv_heads=2, dim=70, vdim=40, conv=5)),
     "pair-delta-head-132": U.parallel(right=U.delta(heads=1, kv_heads=1, dim=132, vdim=8)),
-    "pair-delta-head-beyond-registers": U.parallel(right=U.delta(heads=1, kv_heads=1, dim=70, vdim=520, conv=2)),
+    "pair-delta-head-beyond-registers": U.parallel(right=U.delta(heads=1, kv_heads=1, dim=40, vdim=520, conv=2)),
     "pair-unequal-scaling": U.parallel(left=U.attention(heads=2, kv_heads=1, dim=16, vdim=4, dims=12,
                                                         scaling={"factor": 16.0, "original": 40, "fast": 4.0, "slow": 2.0})),
 }
