@@ -256,8 +256,10 @@ int ssdk_verify(const void* logits_p, const void* logits_q, const int64_t* specu
 
 /* ---- layered ("hybrid") models ---------------------------------------------------
  * A second model family beside the dense Llama / Qwen3 decoders above: a program of layers, each one token mixer
- * (a recurrent matrix-state layer or latent attention) and an optional mixture-of-experts feed-forward that read the
- * SAME normed input (parallel block), with per-channel layer scales.  The reference has no such model; these entry
+ * (a recurrent layer, latent attention, or grouped-query attention beside a delta rule) and an optional feed-forward.
+ * Two block kinds (SSDK_BLOCK_*): mixer and mixture of experts read the SAME normed input and join the residual
+ * stream through per-channel layer scales (parallel pre-norm), or each sublayer reads the residual stream itself and
+ * its OUTPUT is normed before it is added (serial post-norm).  The reference has no such model; these entry
  * points follow the conventions of the ones above (caller-owned device memory, int return codes).
  * Storage type T of weights / activations / latent cache: bf16 (fp32 accumulation; residual stream, norms, routers,
  * attention scores, gates and recurrent state in fp32) or fp32 throughout (no TF32). */

@@ -164,6 +164,7 @@ __global__ void __launch_bounds__(kGqaDecWarps * 32) gqa_decode_partial_kernel(c
       const T* kr = (const T*)p.cache + prow * roww + (size_t)g * D;
       float a0 = 0.f, a1 = 0.f;
       if (vec_k) {
+#pragma unroll 4
         for (int d = 0; d < D; d += kPer) {
           float f[kPer];
           ld_contig<T, kPer>(kr + d, f);
@@ -188,22 +189,27 @@ __global__ void __launch_bounds__(kGqaDecWarps * 32) gqa_decode_partial_kernel(c
     for (int i = 0; i < VPL; ++i) acc[i] *= r;
     mx = m_new;
     const int nk = min(32, k_hi - k0);
-    for (int kk = 0; kk < nk; ++kk) {
-      const float wk = __shfl_sync(0xffffffffu, w, kk);
-      const unsigned long long pr = __shfl_sync(0xffffffffu, (unsigned long long)prow, kk);
-      const T* vr = (const T*)p.cache + (size_t)pr * roww + (size_t)G * D + (size_t)g * V + c0;
-      if (vec_v) {
-        if (c0 < V) {
-          float f[VPL];
-          ld_contig<T, VPL>(vr, f);
+    // eight keys' value rows are requested before any of them is used
+    for (int kk0 = 0; kk0 < nk; kk0 += 8) {
+      float f[8][VPL], wk[8];
 #pragma unroll
-          for (int i = 0; i < VPL; ++i) acc[i] = fmaf(wk, f[i], acc[i]);
+      for (int u = 0; u < 8; ++u) {
+        const int kk = kk0 + u;  // (a lane index below 32 in every case: nk <= 32 and kk0 is a multiple of 8)
+        wk[u] = __shfl_sync(0xffffffffu, w, kk);
+        const unsigned long long pr = __shfl_sync(0xffffffffu, (unsigned long long)prow, kk);
+        const T* vr = (const T*)p.cache + (size_t)pr * roww + (size_t)G * D + (size_t)g * V + c0;
+        const bool live = kk < nk && c0 < V;
+        if (live && vec_v) {
+          ld_contig<T, VPL>(vr, f[u]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < VPL; ++i) f[u][i] = (live && c0 + i < V) ? ld_f<T>(vr + i) : 0.f;
         }
-      } else {
-#pragma unroll
-        for (int i = 0; i < VPL; ++i)
-          if (c0 + i < V) acc[i] = fmaf(wk, ld_f<T>(vr + i), acc[i]);
       }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) acc[i] = fmaf(wk[u], f[u][i], acc[i]);
     }
   }
   float* mine = wp + (size_t)warp * (V + 2);

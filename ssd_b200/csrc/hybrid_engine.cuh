@@ -599,7 +599,7 @@ struct HybRun {
         if (h_cu[s + 1] - h_cu[s] == 1) { ++n_dec; ctx_max = std::max(ctx_max, h_pos0[s] + 1); }
       const int vpl = (V + 31) / 32;
       if (n_dec > 0 && vpl <= 8 && e->use_decode_attn) {
-        int splits = std::max(1, std::min({32, 2 * num_sms() / std::max(1, n_dec * H), (ctx_max + 127) / 128}));
+        int splits = std::max(1, std::min({32, 8 * num_sms() / std::max(1, n_dec * H), (ctx_max + 127) / 128}));  // ~8 four-warp CTAs per SM
         const size_t per_split = (size_t)rg.n_seqs * H * (V + 2);
         splits = (int)std::min<size_t>(splits, e->att_elems / per_split);
         if (splits >= 1) {
