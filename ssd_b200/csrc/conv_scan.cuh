@@ -277,31 +277,39 @@ struct DeltaPrepArgs {
   float q_scale, unit_eps;
 };
 
-// grid (M); dynamic shared memory: (2 G D + H V) floats
+// grid (M, 2 G + H): unit u < G is a query head, u < 2 G a key head, the rest value heads; one CTA convolves the unit's
+// channels (SiLU), and makes a query or key head a unit vector.  dynamic shared memory: max(D, V) floats.
 template <typename T>
 __global__ void delta_prep_kernel(const DeltaPrepArgs p, const Ragged rg) {
   extern __shared__ float dp_sm[];
-  const int m = blockIdx.x, s = rg.tok_seq[m], t = m - rg.cu[s];
-  const int GD = p.G * p.D, HV = p.H * p.V, C = 2 * GD + HV;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) dp_sm[c] = silu_f(conv_at<T>(p.conv, rg, m, s, t, c));
-  for (int h = threadIdx.x; h < p.H; h += blockDim.x) {
-    p.beta[(size_t)m * p.H + h] = sigmoid_f(p.ba[(size_t)m * p.ld_ba + h]);
-    const float sp = softplus_f(p.ba[(size_t)m * p.ld_ba + p.H + h] + ld_f<T>((const T*)p.dt_bias + h));
-    p.decay[(size_t)m * p.H + h] = expf(-expf(ld_f<T>((const T*)p.A_log + h)) * sp);
+  __shared__ float red[33];
+  const int m = blockIdx.x, unit = blockIdx.y, s = rg.tok_seq[m], t = m - rg.cu[s];
+  const int GD = p.G * p.D, HV = p.H * p.V;
+  if (unit == 0) {
+    for (int h = threadIdx.x; h < p.H; h += blockDim.x) {
+      p.beta[(size_t)m * p.H + h] = sigmoid_f(p.ba[(size_t)m * p.ld_ba + h]);
+      const float sp = softplus_f(p.ba[(size_t)m * p.ld_ba + p.H + h] + ld_f<T>((const T*)p.dt_bias + h));
+      p.decay[(size_t)m * p.H + h] = expf(-expf(ld_f<T>((const T*)p.A_log + h)) * sp);
+    }
   }
-  __syncthreads();
-  for (int c = threadIdx.x; c < HV; c += blockDim.x) p.v[(size_t)m * HV + c] = dp_sm[2 * GD + c];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  for (int unit = warp; unit < 2 * p.G; unit += nw) {  // units 0 .. G-1: query heads, G .. 2G-1: key heads
-    const float* src = dp_sm + (size_t)unit * p.D;
-    float ss = 0.f;
-    for (int d = lane; d < p.D; d += 32) ss = fmaf(src[d], src[d], ss);
-    ss = warp_sum(ss);
-    const bool is_q = unit < p.G;
-    const float inv = (is_q ? p.q_scale : 1.0f) / sqrtf(ss + p.unit_eps);
-    float* dst = (is_q ? p.q : p.k) + (size_t)m * GD + (size_t)(is_q ? unit : unit - p.G) * p.D;
-    for (int d = lane; d < p.D; d += 32) dst[d] = src[d] * inv;
+  if (unit >= 2 * p.G) {  // a value head: convolution and SiLU only
+    const int c0 = 2 * GD + (unit - 2 * p.G) * p.V;
+    for (int d = threadIdx.x; d < p.V; d += blockDim.x)
+      p.v[(size_t)m * HV + (size_t)(unit - 2 * p.G) * p.V + d] = silu_f(conv_at<T>(p.conv, rg, m, s, t, c0 + d));
+    return;
   }
+  const int c0 = unit * p.D;  // q heads, then k heads, in the order of the convolution's channels
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < p.D; d += blockDim.x) {
+    const float v = silu_f(conv_at<T>(p.conv, rg, m, s, t, c0 + d));
+    dp_sm[d] = v;
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, red);
+  const bool is_q = unit < p.G;
+  const float inv = (is_q ? p.q_scale : 1.0f) / sqrtf(ss + p.unit_eps);
+  float* dst = (is_q ? p.q : p.k) + (size_t)m * GD + (size_t)(is_q ? unit : unit - p.G) * p.D;
+  for (int d = threadIdx.x; d < p.D; d += blockDim.x) dst[d] = dp_sm[d] * inv;
 }
 
 struct DeltaArgs {

@@ -659,7 +659,8 @@ struct HybRun {
     dp.ba = e->p0 + o_b; dp.ld_ba = Ntot; dp.A_log = Lr.t[SSDK_HT_DELTA_ALOG].p; dp.dt_bias = Lr.t[SSDK_HT_DELTA_DT_B].p;
     dp.q = e->p2; dp.k = dp.q + (size_t)M * dGD; dp.v = dp.k + (size_t)M * dGD; dp.beta = dp.v + (size_t)M * dHV; dp.decay = dp.beta + (size_t)M * Hd;
     dp.H = Hd; dp.G = Gd; dp.D = Dd; dp.V = Vd; dp.q_scale = 1.0f / sqrtf((float)Dd); dp.unit_eps = 1e-6f;
-    CKI(L.go(ssdk::delta_prep_kernel<T>, dim3(M), dim3(256), (size_t)Cd * 4, dp, rg));
+    CKI(L.go(ssdk::delta_prep_kernel<T>, dim3(M, 2 * Gd + Hd), dim3(std::min(256, (std::max(Dd, Vd) + 31) / 32 * 32)),
+             (size_t)std::max(Dd, Vd) * 4, dp, rg));
     CKI(L.go(ssdk::conv_state_kernel<T>, dim3(rg.n_seqs, (Cd + 255) / 256), dim3(256), 0, dp.conv, rg));
     ssdk::DeltaArgs da;
     da.q = dp.q; da.k = dp.k; da.v = dp.v; da.beta = dp.beta; da.decay = dp.decay; da.o = e->p1; da.S = st; da.slot_stride = e->slot_floats;
