@@ -331,10 +331,12 @@ inline size_t delta_scan_smem(int D, int Vr, int DR, int G) {
 
 // grid (n_seqs, H, column splits), block (Vr, G) with Vr a multiple of 32 columns per CTA (the columns of the state are
 // independent of one another, so a head may be spread over several CTAs): thread (j, gi) owns rows [gi DR, (gi + 1) DR)
-// of one column of the head's D x V state, in registers; k and q are read from shared memory four rows at a time.  Both contractions over D (S^T k and S^T q) are thread-local sums over
-// the thread's rows; with G > 1 the row groups' partial sums meet in shared memory and are added in group order (two
-// CTA barriers per row, none with G == 1).  Padded rows meet k = q = 0.  DR == 0: any D, one group, the column lives in
-// shared memory.  Everything is fp32 whatever the model's storage type.
+// of one column of the head's D x V state, in registers.  The rows' k, q, v, beta and decay arrive by cp.async, sixteen
+// rows at a time, under the walk of the previous sixteen; k and q are read from shared memory four rows at a time.
+// Both contractions over D (S^T k and S^T q) are thread-local sums over the thread's rows; with G > 1 the row groups'
+// partial sums meet in shared memory and are added in group order (two CTA barriers per row, none with G == 1).
+// Padded rows meet k = q = 0.  DR == 0: any D, one group, the column lives in shared memory.  Everything is fp32
+// whatever the model's storage type.
 template <int DR>
 __global__ void delta_scan_kernel(const DeltaArgs p, const Ragged rg) {
   extern __shared__ __align__(16) float ds_sm[];

@@ -1,6 +1,6 @@
 """Kefurax through libssdk (HybridRunner / LLM) against the plain float64 oracle of tests/kefurax_plain.py, on small
 random checkpoints of sizes of their own.  float32 storage is the sharp comparison (a wrong key, tap, edge or state shows
-as an error of 1e-2 .. 1, rounding as 1e-6); bfloat16 runs check the product kernels' rounding contract."""
+as an error of 1e-2 .. 1, rounding as 1e-6); bfloat16 runs check what the product kernels round."""
 import numpy as np
 import pytest
 import torch
